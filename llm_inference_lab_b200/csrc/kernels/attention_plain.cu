@@ -13,7 +13,9 @@
 // 1/sqrt(d), mask key <= query, online softmax with max/sum/accumulator in 32-bit,
 // o = acc / sum), 898-942 (merge of partial softmax states).  The window (keys with
 // query - key < window; a negative `window` means chunks of that many positions, see
-// `lab_first_key`) is this engine's addition.
+// `lab_first_key`) is this engine's addition, and so are two options of a window: `keep_first` (the first
+// that many positions stay visible to every later query, at their true positions) and `sink` (1: one is
+// added to the softmax's denominator, a key with score 0 and no value).
 #include "common.cuh"
 
 namespace {
@@ -25,7 +27,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_plain_kernel(
     T* __restrict__ out, int out_stride, const T* __restrict__ q, int q_stride, const T* __restrict__ cache_k,
     const T* __restrict__ cache_v, const int* __restrict__ row_req, const int* __restrict__ row_pos,
     const int* __restrict__ block_table, int max_blocks, int n_q, int n_kv, int d, int page_size, int num_pages,
-    int window, float scale) {
+    int window, float scale, int keep_first, int sink) {
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
@@ -44,9 +46,14 @@ __global__ void __launch_bounds__(WARPS * 32) attention_plain_kernel(
 #pragma unroll
   for (int i = 0; i < MAX_DPL; ++i) acc[i] = 0.f;
 
-  for (int c = first / 32 + warp; c * 32 <= p; c += WARPS) {
+  // two runs of keys: the kept first positions that lie before the window (none without one), then the
+  // window itself; each run cut into chunks by absolute position
+  const int kept_end = window > 0 && keep_first > 0 ? min(keep_first, first) : 0;
+  for (int run = kept_end > 0 ? 0 : 1; run < 2; ++run) {
+  const int lo = run == 0 ? 0 : first, hi = run == 0 ? kept_end - 1 : p;
+  for (int c = lo / 32 + warp; c * 32 <= hi; c += WARPS) {
     const int j = c * 32 + lane;
-    const bool valid = j >= first && j <= p;
+    const bool valid = j >= lo && j <= hi;
     long long base = -1;
     float s = -INFINITY;
     if (valid) {
@@ -81,6 +88,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_plain_kernel(
     }
     m = m_new;
   }
+  }
 
   float* mine = part + warp * (d + 2);
 #pragma unroll
@@ -95,8 +103,9 @@ __global__ void __launch_bounds__(WARPS * 32) attention_plain_kernel(
   __syncthreads();
   float big = -INFINITY;
   for (int w = 0; w < WARPS; ++w) big = fmaxf(big, part[w * (d + 2) + d]);
+  if (sink) big = fmaxf(big, 0.f);
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    float num = 0.f, den = 0.f;
+    float num = 0.f, den = sink ? expf(-big) : 0.f;
     for (int w = 0; w < WARPS; ++w) {
       const float mw = part[w * (d + 2) + d];
       const float wt = (mw == -INFINITY) ? 0.f : expf(mw - big);
@@ -111,7 +120,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_plain_kernel(
 LAB_EXPORT int lab_attention_plain(void* out, int out_stride, const void* q, int q_stride, const void* cache_k,
                                    const void* cache_v, const int* row_req, const int* row_pos, const int* block_table,
                                    int max_blocks, int tokens, int n_q, int n_kv, int d, int page_size, int num_pages,
-                                   int window, float scale, int dtype, cudaStream_t stream) {
+                                   int window, float scale, int keep_first, int sink, int dtype,
+                                   cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (d > 32 * MAX_DPL || d <= 0 || n_q % n_kv) return (int)cudaErrorInvalidValue;
   dim3 grid(tokens, n_q);
@@ -119,9 +129,10 @@ LAB_EXPORT int lab_attention_plain(void* out, int out_stride, const void* q, int
   if (dtype == LAB_F32)
     return (int)lab_launch(attention_plain_kernel<float>, grid, dim3(WARPS * 32), smem, stream, (float*)out, out_stride,
                            (const float*)q, q_stride, (const float*)cache_k, (const float*)cache_v, row_req, row_pos,
-                           block_table, max_blocks, n_q, n_kv, d, page_size, num_pages, window, scale);
+                           block_table, max_blocks, n_q, n_kv, d, page_size, num_pages, window, scale, keep_first,
+                           sink);
   return (int)lab_launch(attention_plain_kernel<__nv_bfloat16>, grid, dim3(WARPS * 32), smem, stream,
                          (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
                          (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v, row_req, row_pos, block_table,
-                         max_blocks, n_q, n_kv, d, page_size, num_pages, window, scale);
+                         max_blocks, n_q, n_kv, d, page_size, num_pages, window, scale, keep_first, sink);
 }

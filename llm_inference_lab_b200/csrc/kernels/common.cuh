@@ -90,6 +90,14 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.0f + tanhf(inner));
 }
 
+// The activation a plain product's epilogue may apply, by its code: 1 the tanh form of GELU, 2 the square of
+// relu (max(z, 0)^2).
+__device__ __forceinline__ float lab_act(float z, int code) {
+  if (code == 1) return gelu_tanh_f(z);
+  const float r = fmaxf(z, 0.f);
+  return r * r;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);

@@ -18,13 +18,22 @@ template <typename T, typename OutT, bool GATED>
 __global__ void __launch_bounds__(256) gemm_plain_kernel(OutT* __restrict__ out, const T* __restrict__ x,
                                                          const T* __restrict__ w, const T* __restrict__ bias, int M,
                                                          int N, int K, int ldx, int ldo, long long batch_x,
-                                                         long long batch_w, long long batch_o, int gelu) {
+                                                         long long batch_w, long long batch_o, int gelu,
+                                                         const int* __restrict__ row_src, int row_div,
+                                                         const int* __restrict__ tile_group) {
   pdl_trigger();
   pdl_wait();
   // a batch of products of one shape (blockIdx.z): operand b lies b * batch_* elements further on
   x += blockIdx.z * batch_x;
   w += blockIdx.z * batch_w;
   out += blockIdx.z * batch_o;
+  // grouped rows: every tile of BM rows meets the matrix of its own group (tile_group[tile], -1: a tile without
+  // rows), batch_w elements apart; row m reads x's row row_src[m] / row_div (-1: a row of padding, zeros)
+  if (tile_group != nullptr) {
+    const int group = tile_group[blockIdx.y];
+    if (group < 0) return;
+    w += (long long)group * batch_w;
+  }
   __shared__ float xs[BK][BM + PAD];
   __shared__ float ws[GATED ? 2 : 1][BK][BN + PAD];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
@@ -38,11 +47,15 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(OutT* __restrict__ out,
       for (int j = 0; j < 4; ++j) acc[g][i][j] = 0.f;
 
   const int lr = tid >> 2, lk = (tid & 3) * 4;  // this thread loads row lr, k in [lk, lk + 4)
+  int m = m0 + lr;                              // the row of x this thread loads
+  if (row_src != nullptr && m < M) {
+    const int src = row_src[m];
+    m = src < 0 ? M : src / row_div;
+  }
   for (int k0 = 0; k0 < K; k0 += BK) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int k = k0 + lk + e;
-      const int m = m0 + lr;
       xs[lk + e][lr] = (m < M && k < K) ? to_f32<T>(x[(size_t)m * ldx + k]) : 0.f;
       const int n = n0 + lr;
       ws[0][lk + e][lr] = (n < N && k < K) ? to_f32<T>(w[(size_t)n * K + k]) : 0.f;
@@ -81,7 +94,7 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(OutT* __restrict__ out,
         v = g / (1.f + expf(-g)) * u;
       } else {
         v = acc[0][i][j] + (bias ? to_f32<T>(bias[n]) : 0.f);
-        if (gelu) v = gelu_tanh_f(v);      // the tanh form of GELU after the bias, before the rounding
+        if (gelu) v = lab_act(v, gelu);      // the activation after the bias, before the rounding
       }
       out[(size_t)m * ldo + n] = from_f32<OutT>(v);
     }
@@ -133,18 +146,21 @@ int launch_heads_few(void* out, const void* x, const void* w, int M, int N, int 
 
 template <typename T, typename OutT>
 int launch(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx, int ldo, int gated,
-           cudaStream_t stream, int batch = 1, long long batch_x = 0, long long batch_w = 0, long long batch_o = 0) {
+           cudaStream_t stream, int batch = 1, long long batch_x = 0, long long batch_w = 0, long long batch_o = 0,
+           const int* row_src = nullptr, int row_div = 1, const int* tile_group = nullptr) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
   if (gated == 1)
     return (int)lab_launch(gemm_plain_kernel<T, OutT, true>, grid, dim3(256), 0, stream, (OutT*)out, (const T*)x,
-                           (const T*)w, (const T*)nullptr, M, N, K, ldx, ldo, batch_x, batch_w, batch_o, 0);
+                           (const T*)w, (const T*)nullptr, M, N, K, ldx, ldo, batch_x, batch_w, batch_o, 0, row_src,
+                           row_div, tile_group);
   return (int)lab_launch(gemm_plain_kernel<T, OutT, false>, grid, dim3(256), 0, stream, (OutT*)out, (const T*)x,
-                         (const T*)w, (const T*)bias, M, N, K, ldx, ldo, batch_x, batch_w, batch_o, gated == 2 ? 1 : 0);
+                         (const T*)w, (const T*)bias, M, N, K, ldx, ldo, batch_x, batch_w, batch_o,
+                         gated >= 2 ? gated - 1 : 0, row_src, row_div, tile_group);
 }
 }  // namespace
 
 // N is the number of output columns; with gated == 1, w holds 2 N rows (gate rows, then up rows); gated == 2 is
-// the plain product with GELU (tanh form) after the bias.
+// the plain product with GELU (tanh form) after the bias, 3 with the square of relu.
 LAB_EXPORT int lab_gemm_plain(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx,
                               int ldo, int gated, int dtype, int out_f32, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
@@ -174,4 +190,24 @@ LAB_EXPORT int lab_gemm_plain_batched(void* out, const void* x, const void* w, i
                                         batch_o);
   return launch<__nv_bfloat16, __nv_bfloat16>(out, x, w, nullptr, M, N, K, ldx, ldo, 0, stream, batch, batch_x, batch_w,
                                               batch_o);
+}
+
+// Rows grouped by the matrix they meet (routed experts): tile t of lab_gemm_plain_group_rows() rows meets the
+// matrix tile_group[t] of `w` (matrices group_w elements apart; -1: the tile holds no rows and is skipped); row m of
+// the product reads x's row row_src[m] / row_div (row_src null: row m itself; -1: padding, read as zeros).
+// M counts the rows of the grouped layout (out has that many); x must hold every row that row_src names.
+LAB_EXPORT int lab_gemm_plain_group_rows() { return BM; }
+LAB_EXPORT int lab_gemm_plain_grouped(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
+                                      int gated, long long group_w, const int* row_src, int row_div,
+                                      const int* tile_group, int dtype, int out_f32, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (tile_group == nullptr || row_div < 1) return (int)cudaErrorInvalidValue;
+  if (dtype == LAB_F32)
+    return launch<float, float>(out, x, w, nullptr, M, N, K, ldx, ldo, gated, stream, 1, 0, group_w, 0, row_src, row_div,
+                                tile_group);
+  if (out_f32)
+    return launch<__nv_bfloat16, float>(out, x, w, nullptr, M, N, K, ldx, ldo, gated, stream, 1, 0, group_w, 0, row_src,
+                                        row_div, tile_group);
+  return launch<__nv_bfloat16, __nv_bfloat16>(out, x, w, nullptr, M, N, K, ldx, ldo, gated, stream, 1, 0, group_w, 0,
+                                              row_src, row_div, tile_group);
 }

@@ -99,7 +99,7 @@ struct Params {
   void* out;            // [tokens, ld_out] of OutT, or partial [splits, tokens, ld_out] floats;
                         // q/k/v: the rotated q [tokens, ld_out]
   const __nv_bfloat16* bias;
-  int gelu;             // plain epilogue: the tanh form of GELU after the bias, before the rounding
+  int gelu;             // plain epilogue, after the bias and before the rounding: 1 the tanh form of GELU, 2 relu squared
   int m_rows;           // valid rows on the M side (tokens, or features when swapped)
   int n_rows;           // valid rows on the N side
   int ld_out;
@@ -525,7 +525,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             }
             if (p.gelu) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_f(v[j]);
+              for (int j = 0; j < 32; ++j) v[j] = lab_act(v[j], p.gelu);
             }
             OutT* dst = (OutT*)p.out + (size_t)m * p.ld_out + n;
             if (n + 32 <= p.n_rows && (((uintptr_t)dst) & 15) == 0) {
@@ -606,7 +606,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
 #pragma unroll
             for (int j = 0; j < 16; ++j)
               if (t + j < p.n_rows)
-                dst[(size_t)(t + j) * p.ld_out] = from_f32<OutT>(p.gelu ? gelu_tanh_f(v[j] + b) : v[j] + b);
+                dst[(size_t)(t + j) * p.ld_out] = from_f32<OutT>(p.gelu ? lab_act(v[j] + b, p.gelu) : v[j] + b);
           }
         }
         release();
@@ -762,12 +762,12 @@ __global__ void wait_probe_kernel(unsigned long long limit_ns, int* gave_up) {
 // out: bf16 or f32 [tokens, ld_out]; with splits > 1, `out` is the partial buffer
 // [splits, tokens, ld_out] of floats (no bias, not gated).
 // swap != 0: features on the M side (few tokens); bn: tile of the N side (16..256).
-// gated: 0 the plain product, 1 the SiLU-gated pair, 2 the plain product with GELU (tanh form) after the bias.
+// gated: 0 the plain product, 1 the SiLU-gated pair, 2 the plain product with GELU (tanh form) after the bias, 3 with the square of relu.
 LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* bias, int tokens, int n_out, int K,
                            int ldx, int ld_out, int gated, int out_f32, int swap, int bn, int splits,
                            cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
-  const int gelu = gated == 2;
+  const int gelu = gated >= 2 ? gated - 1 : 0;      // 1: GELU, 2: the square of relu
   if (gelu) gated = 0;
   if (gelu && splits > 1) return (int)cudaErrorInvalidValue;
   if (K % 8 || ldx % 8 || K <= 0) return (int)cudaErrorInvalidValue;            // 16-byte rows for TMA

@@ -92,7 +92,7 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a,
 struct Params {
   void* out;            // [tokens, ld_out] of OutT, or partial [splits, tokens, ld_out] floats
   const __nv_bfloat16* bias;
-  int gelu;             // plain epilogue: the tanh form of GELU after the bias, before the rounding
+  int gelu;             // plain epilogue, after the bias and before the rounding: 1 the tanh form of GELU, 2 relu squared
   int tokens, n_out;    // valid rows and output features
   int ld_out;
   long long split_stride;  // elements between split-K partial planes (0: no split)
@@ -295,7 +295,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
           }
           if (p.gelu) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_f(v[j]);
+            for (int j = 0; j < 32; ++j) v[j] = lab_act(v[j], p.gelu);
           }
           OutT* dst = (OutT*)p.out + (size_t)m * p.ld_out + n;
           const bool aligned = (((uintptr_t)dst) & 15) == 0;
@@ -426,11 +426,11 @@ int pick_bn(int tokens, int n_out, bool gated, int splits) {
 // out: bf16 or f32 [tokens, ld_out]; with splits > 1, `out` is the partial buffer
 // [splits, tokens, ld_out] of floats (no bias, not gated).
 // bn: accumulator columns of a tile, 256, 224 or 192; 0: the width that fills the rounds of the pairs best.
-// gated: 0 the plain product, 1 the SiLU-gated pair, 2 the plain product with GELU (tanh form) after the bias.
+// gated: 0 the plain product, 1 the SiLU-gated pair, 2 the plain product with GELU (tanh form) after the bias, 3 with the square of relu.
 LAB_EXPORT int lab_gemm_tc2(void* out, const void* x, const void* w, const void* bias, int tokens, int n_out, int K,
                             int ldx, int ld_out, int gated, int out_f32, int splits, int bn, cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
-  const int gelu = gated == 2;
+  const int gelu = gated >= 2 ? gated - 1 : 0;      // 1: GELU, 2: the square of relu
   if (gelu) gated = 0;
   if (gelu && splits > 1) return (int)cudaErrorInvalidValue;
   if (K % 8 || ldx % 8 || K <= 0) return (int)cudaErrorInvalidValue;            // 16-byte rows for TMA

@@ -7,7 +7,7 @@
 // the softmax's denominator as exp(sink) with no key, no value and no scaling.
 //
 // Kernels: the preparation of a step's rows (two RMS norms with plain weights, the rotation of
-// the shared key part, the write into the page slots), the rotation of the queries' rotated
+// the shared key part, by halves or by neighbouring pairs, the write into the page slots), the rotation of the queries' rotated
 // parts, and the attention itself.  Scores, softmax weights, angles and norms are 32-bit;
 // T says how the cache and the outputs that feed matrix products are stored.
 #include "common.cuh"
@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(kThreads) latent_prep_kernel(T* __restrict__ c
                                                                const int* __restrict__ positions,
                                                                const float* __restrict__ inv_freq, int rot_dims,
                                                                const int* __restrict__ slots, long long n_slots,
-                                                               float eps) {
+                                                               float eps, int pairs) {
   __shared__ float scratch[32];
   pdl_trigger();
   pdl_wait();
@@ -40,7 +40,7 @@ __global__ void __launch_bounds__(kThreads) latent_prep_kernel(T* __restrict__ c
   for (int i = threadIdx.x; i < C; i += kThreads) sc += row[Q + i] * row[Q + i];
   sq = block_sum(sq, scratch);
   sc = block_sum(sc, scratch);
-  const float iq = 1.0f / sqrtf(sq / (float)Q + eps), ic = 1.0f / sqrtf(sc / (float)C + eps);
+  const float iq = Q > 0 ? 1.0f / sqrtf(sq / (float)Q + eps) : 0.f, ic = 1.0f / sqrtf(sc / (float)C + eps);
   for (int i = threadIdx.x; i < Q; i += kThreads) cq[(size_t)t * Q + i] = from_f32<T>(row[i] * iq * to_f32(wq[i]));
   if (cache == nullptr) return;
   const long long slot = slots[t];
@@ -57,12 +57,14 @@ __global__ void __launch_bounds__(kThreads) latent_prep_kernel(T* __restrict__ c
   for (int i = threadIdx.x; i < R; i += kThreads) {
     float v = kr[i];
     if (i < rot_dims) {
-      const int f = i < half ? i : i - half;
+      // entry f of the frequencies turns the pair (f, f + half), or with `pairs` the neighbours (2f, 2f + 1)
+      const int f = pairs ? i >> 1 : (i < half ? i : i - half);
+      const bool first = pairs ? !(i & 1) : i < half;
       const float ang = pos * inv_freq[f];
       const float cs = cosf(ang), sn = sinf(ang);
       float lo, hi;
-      rope_rotate(kr[f], kr[f + half], cs, sn, lo, hi);
-      v = i < half ? lo : hi;
+      rope_rotate(kr[pairs ? 2 * f : f], kr[pairs ? 2 * f + 1 : f + half], cs, sn, lo, hi);
+      v = first ? lo : hi;
     }
     dst[C + i] = from_f32<T>(v);
   }
@@ -78,7 +80,7 @@ __global__ void __launch_bounds__(kThreads) latent_q_rope_kernel(float* __restri
                                                                  int heads, int D, int R, int C, int q_head,
                                                                  const int* __restrict__ positions,
                                                                  const float* __restrict__ inv_freq, int rot_dims,
-                                                                 int in_place) {
+                                                                 int in_place, int pairs) {
   extern __shared__ float rotated[];      // [heads * R]
   pdl_trigger();
   pdl_wait();
@@ -90,12 +92,13 @@ __global__ void __launch_bounds__(kThreads) latent_q_rope_kernel(float* __restri
     const T* src = q + ((size_t)t * heads + h) * q_head + D;
     float v = to_f32(src[i]);
     if (i < rot_dims) {
-      const int f = i < half ? i : i - half;
+      const int f = pairs ? i >> 1 : (i < half ? i : i - half);
+      const bool first = pairs ? !(i & 1) : i < half;
       const float ang = pos * inv_freq[f];
       const float cs = cosf(ang), sn = sinf(ang);
       float lo, hi;
-      rope_rotate(to_f32(src[f]), to_f32(src[f + half]), cs, sn, lo, hi);
-      v = i < half ? lo : hi;
+      rope_rotate(to_f32(src[pairs ? 2 * f : f]), to_f32(src[pairs ? 2 * f + 1 : f + half]), cs, sn, lo, hi);
+      v = first ? lo : hi;
     }
     if (q_cat != nullptr) q_cat[((size_t)t * heads + h) * (C + R) + C + i] = v;
     rotated[idx] = v;
@@ -396,31 +399,31 @@ bool attention_shape(int heads, int C, int W, int max_q, int* qt_out, int* hg_ou
 
 LAB_EXPORT int lab_latent_prep(void* cq, void* cache, const float* proj, int ld, int Q, int C, int R, const void* wq,
                                const void* wc, const int* positions, const float* inv_freq, int rot_dims,
-                               const int* slots, long long n_slots, int tokens, float eps, int dtype,
+                               const int* slots, long long n_slots, int tokens, float eps, int pairs, int dtype,
                                cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (dtype == LAB_F32)
     lab_launch(latent_prep_kernel<float>, dim3(tokens), dim3(kThreads), 0, stream, (float*)cq, (float*)cache, proj, ld,
-               Q, C, R, (const float*)wq, (const float*)wc, positions, inv_freq, rot_dims, slots, n_slots, eps);
+               Q, C, R, (const float*)wq, (const float*)wc, positions, inv_freq, rot_dims, slots, n_slots, eps, pairs);
   else
     lab_launch(latent_prep_kernel<__nv_bfloat16>, dim3(tokens), dim3(kThreads), 0, stream, (__nv_bfloat16*)cq,
                (__nv_bfloat16*)cache, proj, ld, Q, C, R, (const __nv_bfloat16*)wq, (const __nv_bfloat16*)wc, positions,
-               inv_freq, rot_dims, slots, n_slots, eps);
+               inv_freq, rot_dims, slots, n_slots, eps, pairs);
   LAB_LAUNCH_CHECK();
 }
 
 LAB_EXPORT int lab_latent_q_rope(float* q_cat, void* q, int tokens, int heads, int D, int R, int C, int q_head,
-                                 const int* positions, const float* inv_freq, int rot_dims, int in_place, int dtype,
-                                 cudaStream_t stream) {
+                                 const int* positions, const float* inv_freq, int rot_dims, int in_place, int pairs,
+                                 int dtype, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const size_t smem = sizeof(float) * (size_t)heads * R;
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
   if (dtype == LAB_F32)
     lab_launch(latent_q_rope_kernel<float>, dim3(tokens), dim3(kThreads), smem, stream, q_cat, (float*)q, heads, D, R, C,
-               q_head, positions, inv_freq, rot_dims, in_place);
+               q_head, positions, inv_freq, rot_dims, in_place, pairs);
   else
     lab_launch(latent_q_rope_kernel<__nv_bfloat16>, dim3(tokens), dim3(kThreads), smem, stream, q_cat,
-               (__nv_bfloat16*)q, heads, D, R, C, q_head, positions, inv_freq, rot_dims, in_place);
+               (__nv_bfloat16*)q, heads, D, R, C, q_head, positions, inv_freq, rot_dims, in_place, pairs);
   LAB_LAUNCH_CHECK();
 }
 

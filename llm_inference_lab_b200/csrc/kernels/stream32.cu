@@ -199,11 +199,15 @@ __global__ void __launch_bounds__(kThreads) embed_position_kernel(float* __restr
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
-  int id = ids[t], p = positions[t];
+  int id = ids[t], p = pos_table != nullptr ? positions[t] : 0;
   id = min(max(id, 0), vocab - 1);
+  const T* row = table + (size_t)id * hidden;
+  if (pos_table == nullptr) {      // no learned positions: the table's row as a 32-bit row
+    for (int i = threadIdx.x; i < hidden; i += kThreads) out[(size_t)t * hidden + i] = to_f32(row[i]);
+    return;
+  }
   if (p >= max_positions && threadIdx.x == 0) lab_set_error(LAB_ERR_ROW_RANGE);
   p = min(max(p, 0), max_positions - 1);
-  const T* row = table + (size_t)id * hidden;
   const T* prow = pos_table + (size_t)p * hidden;
   for (int i = threadIdx.x; i < hidden; i += kThreads)
     out[(size_t)t * hidden + i] = to_f32(row[i]) + to_f32(prow[i]);
@@ -212,12 +216,14 @@ __global__ void __launch_bounds__(kThreads) embed_position_kernel(float* __restr
 // ---- x += norm(product): the sum that closes a sublayer whose *output* is normed ----------------
 // y = a[t] (+ bias), a a 32-bit product [tokens, hidden] or split-K partial products summed in ascending
 // order; x[t] += y / rms(y) * w; and (if asked) the new x[t] rounded to T, for the product that reads
-// the stream next.
+// the stream next, or, with `w_next`, the new x[t] normed once more: x[t] / rms(x[t]) * w_next, rounded (the
+// norm that opens the next sublayer, in the same pass).
 template <typename T>
 __global__ void __launch_bounds__(1024) stream_norm_add_kernel(float* __restrict__ x, T* __restrict__ copy,
                                                                const float* __restrict__ a, int a_splits,
                                                                long long split_stride, const T* __restrict__ bias,
-                                                               const T* __restrict__ w, int hidden, float eps) {
+                                                               const T* __restrict__ w, int hidden, float eps,
+                                                               const T* __restrict__ w_next) {
   __shared__ float scratch[32];
   extern __shared__ float row[];      // [hidden]: the product's row, summed once
   pdl_trigger();
@@ -233,11 +239,21 @@ __global__ void __launch_bounds__(1024) stream_norm_add_kernel(float* __restrict
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  float s2 = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     const float v = x[base + i] + row[i] * inv * to_f32(w[i]);
     x[base + i] = v;
-    if (copy != nullptr) copy[base + i] = from_f32<T>(v);
+    if (w_next != nullptr) {
+      row[i] = v;
+      s2 += v * v;
+    } else if (copy != nullptr) {
+      copy[base + i] = from_f32<T>(v);
+    }
   }
+  if (w_next == nullptr || copy == nullptr) return;
+  s2 = block_sum(s2, scratch);
+  const float inv2 = 1.0f / sqrtf(s2 / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) copy[base + i] = from_f32<T>(row[i] * inv2 * to_f32(w_next[i]));
 }
 
 // ---- the stream rounded to T ------------------------------------------------------------------
@@ -372,7 +388,8 @@ LAB_EXPORT int lab_embed_position(float* out, const void* table, const void* pos
 }
 
 LAB_EXPORT int lab_stream_norm_add(float* x, void* copy, const float* a, int a_splits, const void* bias, const void* w,
-                                   int tokens, int hidden, float eps, int dtype, cudaStream_t stream) {
+                                   int tokens, int hidden, float eps, const void* w_next, int dtype,
+                                   cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const long long stride = (long long)tokens * hidden;
   const size_t smem = (size_t)hidden * sizeof(float);
@@ -382,12 +399,13 @@ LAB_EXPORT int lab_stream_norm_add(float* x, void* copy, const float* a, int a_s
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(stream_norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     lab_launch(stream_norm_add_kernel<float>, dim3(tokens), dim3(threads), smem, stream, x, (float*)copy, a, a_splits,
-               stride, (const float*)bias, (const float*)w, hidden, eps);
+               stride, (const float*)bias, (const float*)w, hidden, eps, (const float*)w_next);
   } else {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(stream_norm_add_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     lab_launch(stream_norm_add_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), smem, stream, x, (__nv_bfloat16*)copy,
-               a, a_splits, stride, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)w, hidden, eps);
+               a, a_splits, stride, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)w, hidden, eps,
+               (const __nv_bfloat16*)w_next);
   }
   LAB_LAUNCH_CHECK();
 }

@@ -16,14 +16,16 @@ PYBIND11_MODULE(_lab_runtime, m) {
   py::register_exception<StateError>(m, "StateError", PyExc_RuntimeError);
 
   py::class_<GroupConfig>(m, "GroupConfig")
-      .def(py::init([](int page_size, int window, int num_pages) {
+      .def(py::init([](int page_size, int window, int num_pages, int keep_first) {
              GroupConfig g;
              g.page_size = page_size;
              g.window = window;
              g.num_pages = num_pages;
+             g.keep_first = keep_first;
              return g;
            }),
-           py::arg("page_size"), py::arg("window"), py::arg("num_pages"))
+           py::arg("page_size"), py::arg("window"), py::arg("num_pages"), py::arg("keep_first") = 0)
+      .def_readonly("keep_first", &GroupConfig::keep_first)
       .def_readonly("page_size", &GroupConfig::page_size)
       .def_readonly("window", &GroupConfig::window)
       .def_readonly("num_pages", &GroupConfig::num_pages);

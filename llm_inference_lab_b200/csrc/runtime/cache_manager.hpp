@@ -35,6 +35,7 @@ struct GroupConfig {
   int page_size = 16;
   int window = 0;  // 0: every key is kept; else only the last `window` keys are readable
   int num_pages = 0;
+  int keep_first = 0;  // with a window: the first `keep_first` positions stay readable too, so their pages are never given back
 };
 
 // A stack of free page (or slot) numbers that refuses double frees and unknown numbers.
@@ -98,7 +99,7 @@ class CacheManager {
       : groups_(std::move(groups)), slots_(max_requests) {
     if (max_requests <= 0) throw std::invalid_argument("max_requests must be positive");
     for (auto& g : groups_) {
-      if (g.page_size <= 0 || g.num_pages < 0 || g.window < 0) throw std::invalid_argument("bad group configuration");
+      if (g.page_size <= 0 || g.num_pages < 0 || g.window < 0 || g.keep_first < 0) throw std::invalid_argument("bad group configuration");
       pools_.emplace_back(g.num_pages);
     }
   }
@@ -150,7 +151,7 @@ class CacheManager {
     // Live positions never span more than window - 1 + max_step; such a span touches
     // at most ceil(span / page) + 1 pages.
     const int span = cfg.window - 1 + std::max(1, max_step);
-    return std::min(all, blocks_for(span, cfg.page_size) + 1);
+    return std::min(all, blocks_for(span, cfg.page_size) + 1 + blocks_for(cfg.keep_first, cfg.page_size));
   }
 
   // True if all of `entries` could be reserved together right now.
@@ -191,6 +192,8 @@ class CacheManager {
       if (cfg.window == 0) continue;
       // A later query sits at position >= committed and reads keys > position - window.
       const int first_needed = rc.committed - cfg.window + 1;
+      // blocks that hold one of the first `keep_first` positions stay for the request's whole life
+      rc.first_live[g] = std::max(rc.first_live[g], std::min(blocks_for(cfg.keep_first, cfg.page_size), (int)rc.tables[g].size()));
       while (rc.first_live[g] < (int)rc.tables[g].size() &&
              (rc.first_live[g] + 1) * cfg.page_size <= first_needed) {
         int& page = rc.tables[g][rc.first_live[g]];

@@ -94,7 +94,8 @@ class Engine:
         self.num_pages = -(-int(max_tokens) // self.page_size)
         plan = model.cache_plan
         rt = cache_mod.runtime()
-        groups = [rt.GroupConfig(self.page_size, w, self.num_pages) for w in plan.group_windows]
+        groups = [rt.GroupConfig(self.page_size, w, self.num_pages, keep)
+                  for w, keep in zip(plan.group_windows, plan.group_keeps)]
         self.cache = rt.CacheManager(groups, self.max_requests)
         self.group_windows = list(plan.group_windows)
         self.views: list[CacheView] = []

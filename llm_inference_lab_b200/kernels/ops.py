@@ -280,7 +280,7 @@ def gemm_plain(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = Non
         out = torch.empty((M, N), dtype=odt, device=x.device)
     assert out.dtype == odt and out.stride(1) == 1 and out.shape == (M, N)
     _check(lib("gemm_plain").lab_gemm_plain(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), M, N, K, x.stride(0),
-                                            out.stride(0), 2 if gelu else int(gated), dtype_code(x.dtype), int(out_f32),
+                                            out.stride(0), (1 + int(gelu)) if gelu else int(gated), dtype_code(x.dtype), int(out_f32),
                                             _stream()),
            "gemm_plain")
     return out
@@ -311,8 +311,11 @@ def linear_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.T
 
 def attention_plain(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, row_req: torch.Tensor,
                     row_pos: torch.Tensor, block_table: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
-                    window: int, scale: float, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Attention of every row over its request's pages; q may be a column slice of the fused projection."""
+                    window: int, scale: float, out: torch.Tensor | None = None, keep_first: int = 0,
+                    sink_one: bool = False) -> torch.Tensor:
+    """Attention of every row over its request's pages; q may be a column slice of the fused projection.
+    `keep_first`: with a window, the first that many positions stay visible; `sink_one`: one more in the
+    softmax's denominator."""
     _on_gpu(q, cache_k, cache_v, row_req, row_pos, block_table)
     tokens = q.shape[0]
     if out is None:
@@ -323,7 +326,7 @@ def attention_plain(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tenso
     _check(lib("attention_plain").lab_attention_plain(
         _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_k), _ptr(cache_v), _ptr(row_req), _ptr(row_pos),
         _ptr(block_table), block_table.shape[1], tokens, n_q, n_kv, head_dim, page_size, num_pages, window,
-        ctypes.c_float(scale), dtype_code(q.dtype), _stream()), "attention_plain")
+        ctypes.c_float(scale), int(keep_first), int(bool(sink_one)), dtype_code(q.dtype), _stream()), "attention_plain")
     return out
 
 
@@ -446,7 +449,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, 
     if gelu and (gated or splits > 1):
         raise KernelError("gemm_tc: GELU goes with the plain, unsplit product")
     _check(lib("gemm_tc").lab_gemm_tc(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), T, n_out, K, x.stride(0), ld_out,
-                                      2 if gelu else int(gated), int(f32), int(swap), bn, splits, _stream()), "gemm_tc")
+                                      (1 + int(gelu)) if gelu else int(gated), int(f32), int(swap), bn, splits, _stream()), "gemm_tc")
     return out
 
 
@@ -482,7 +485,7 @@ def gemm_tc2(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     if gelu and (gated or splits > 1):
         raise KernelError("gemm_tc2: GELU goes with the plain, unsplit product")
     _check(lib("gemm_tc2").lab_gemm_tc2(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), T, n_out, K, x.stride(0), ld_out,
-                                        2 if gelu else int(gated), int(f32), splits, bn, _stream()), "gemm_tc2")
+                                        (1 + int(gelu)) if gelu else int(gated), int(f32), splits, bn, _stream()), "gemm_tc2")
     return out
 
 
@@ -615,14 +618,18 @@ def _tc_operands(x, w) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+# activations a plain product applies in its epilogue, with their codes (`gelu` = 1, 2 in the product kernels' faces)
+ACTIVATIONS = {"gelu_tanh": 1, "relu2": 2}
+
+
 def linear(x, w, bias=None, out_f32=False, allow_partial=False, out=None, act=None):
     """x @ w.T (+ bias).  With `allow_partial` the result may come back as 32-bit partial
     products [splits, tokens, out], without the bias, that the consumer sums (`add_rmsnorm`,
     `rope_kv_write`, `stream_add`).  `out`: where the result goes (rows may be strided).  `act`:
-    an activation of the result ("gelu_tanh"), applied after the bias and before the rounding."""
-    gelu = act is not None
-    if gelu and (act != "gelu_tanh" or allow_partial):
+    an activation of the result ("gelu_tanh", or "relu2": the square of relu), applied after the bias and before the rounding."""
+    if act is not None and (act not in ACTIVATIONS or allow_partial):
         raise KernelError(f"linear: activation {act!r} is not built, or asked of partial products")
+    gelu = ACTIVATIONS[act] if act is not None else 0      # the epilogue's code of the activation
     if x.dtype == torch.float32 or _force_plain or not _tc_operands(x, w) or (
             out is not None and (out.stride(0) % 8 or out.data_ptr() % 16)):
         return gemm_plain(x, w, bias, out_f32=out_f32, out=out, gelu=gelu)
@@ -751,14 +758,23 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
     return out
 
 
-def attention(q, cache_k, cache_v, ctx, group, n_q, n_kv, head_dim, window, scale, chunk=0):
+def attention(q, cache_k, cache_v, ctx, group, n_q, n_kv, head_dim, window, scale, chunk=0, keep_first=0,
+              sink_one=False):
     """Causal attention of every row over its request's cached keys: all of them, the last `window`, or
     (with `chunk`) those of the row's own chunk of `chunk` positions, chunks counted from position 0.  The
-    kernels take the mask as one number: a window as it is, a chunk as its negative."""
+    kernels take the mask as one number: a window as it is, a chunk as its negative.  `keep_first`: beside a
+    window, the first that many positions of the sequence stay visible; `sink_one`: the softmax's denominator
+    holds one more (a key with score 0 and no value)."""
     if chunk:
         if window:
             raise KernelError("attention takes a window or a chunk, not both")
         window = -int(chunk)
+    if keep_first and window <= 0:
+        keep_first = 0          # kept first positions only matter beside a window
+    if keep_first or sink_one:
+        # the first positions a window keeps, and the denominator's extra one, are the plain kernel's
+        return attention_plain(q, cache_k, cache_v, ctx.row_req, ctx.row_pos, group.block_table, n_q, n_kv, head_dim,
+                               window, scale, keep_first=keep_first, sink_one=sink_one)
     if q.dtype == torch.bfloat16 and not _force_plain and attention_tc_supported(head_dim):
         return attention_tc(q, cache_k, cache_v, ctx.q_start, ctx.kv_len, ctx.pos0, group.block_table,
                             ctx.n_requests, ctx.q_lens, ctx.max_kv_len, n_q, n_kv, head_dim, window, scale)
@@ -944,30 +960,33 @@ def delta_rule(proj: torch.Tensor, decay_pre: torch.Tensor, decay_bias: torch.Te
 # ----------------------------------------------------------------------------------------
 def latent_prep(proj: torch.Tensor, q_rank: int, kv_rank: int, rot_dim: int, w_q: torch.Tensor, w_c: torch.Tensor,
                 positions: torch.Tensor, inv_freq: torch.Tensor, rot_dims: int, slots: torch.Tensor | None,
-                cache: torch.Tensor | None, eps: float) -> torch.Tensor:
+                cache: torch.Tensor | None, eps: float, pairs: bool = False) -> torch.Tensor:
     """From the 32-bit low-rank projections of a step's rows [tokens, q_rank + kv_rank + rot_dim]: the
-    normalised query latent (returned, in the weights' storage type), and, into each row's cache slot,
+    normalised query latent (returned, in the weights' storage type; None where q_rank is 0: queries
+    projected directly), `pairs`: the rotation turns neighbouring entries (2i, 2i + 1) instead of (i, i + half);
+    and, into each row's cache slot,
     the normalised key/value latent followed by the rotated shared key part (`cache` None: no write)."""
     _on_gpu(proj, w_q, w_c, positions, inv_freq, slots, cache)
     tokens = proj.shape[0]
     assert proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] == q_rank + kv_rank + rot_dim
-    assert w_q.numel() == q_rank and w_c.numel() == kv_rank and w_q.dtype == w_c.dtype
+    assert w_c.numel() == kv_rank and ((q_rank == 0 and w_q is None) or (w_q.numel() == q_rank and w_q.dtype == w_c.dtype))
     assert inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2 and rot_dims <= rot_dim
     n_slots = 0
     if cache is not None:
-        assert cache.is_contiguous() and cache.shape[2] == kv_rank + rot_dim and cache.dtype == w_q.dtype
+        assert cache.is_contiguous() and cache.shape[2] == kv_rank + rot_dim and cache.dtype == w_c.dtype
         assert slots is not None and slots.dtype == torch.int32
         n_slots = cache.shape[0] * cache.shape[1]
-    cq = torch.empty((tokens, q_rank), dtype=w_q.dtype, device=proj.device)
+    cq = torch.empty((tokens, q_rank), dtype=w_c.dtype, device=proj.device) if q_rank else None
     _check(lib("latent_attention").lab_latent_prep(
         _ptr(cq), _ptr(cache), _ptr(proj), proj.stride(0), q_rank, kv_rank, rot_dim, _ptr(w_q), _ptr(w_c),
         _ptr(positions), _ptr(inv_freq), rot_dims, _ptr(slots), ctypes.c_longlong(n_slots), tokens,
-        ctypes.c_float(eps), dtype_code(w_q.dtype), _stream()), "latent_prep")
+        ctypes.c_float(eps), int(bool(pairs)), dtype_code(w_c.dtype), _stream()), "latent_prep")
     return cq
 
 
 def latent_q_rope(q: torch.Tensor, q_cat: torch.Tensor | None, heads: int, dim: int, rot_dim: int, kv_rank: int,
-                  positions: torch.Tensor, inv_freq: torch.Tensor, rot_dims: int, in_place: bool = False) -> None:
+                  positions: torch.Tensor, inv_freq: torch.Tensor, rot_dims: int, in_place: bool = False,
+                  pairs: bool = False) -> None:
     """Rotates entries [dim, dim + rot_dim) of every head of q [tokens, heads * q_head] (q_head >= dim + rot_dim:
     a head may end in padding) into columns [kv_rank, kv_rank + rot_dim) of each head of the 32-bit q_cat
     [tokens, heads, kv_rank + rot_dim]; with `in_place` also into q itself (q_cat may then be None)."""
@@ -980,7 +999,7 @@ def latent_q_rope(q: torch.Tensor, q_cat: torch.Tensor | None, heads: int, dim: 
     assert q_cat is not None or in_place
     _check(lib("latent_attention").lab_latent_q_rope(_ptr(q_cat), _ptr(q), tokens, heads, dim, rot_dim, kv_rank, q_head,
                                                      _ptr(positions), _ptr(inv_freq), rot_dims, int(in_place),
-                                                     dtype_code(q.dtype), _stream()), "latent_q_rope")
+                                                     int(bool(pairs)), dtype_code(q.dtype), _stream()), "latent_q_rope")
 
 
 def latent_attention(q_cat: torch.Tensor, cache: torch.Tensor, sink: torch.Tensor | None, ctx, group, heads: int,
@@ -1085,33 +1104,41 @@ def latent_attention_plain_form(q: torch.Tensor, cache: torch.Tensor, w_up: torc
 # ----------------------------------------------------------------------------------------
 # A 32-bit stream with learned positions and normed sublayer outputs (csrc/kernels/stream32.cu).
 # ----------------------------------------------------------------------------------------
-def embed_position(ids: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, pos_table: torch.Tensor) -> torch.Tensor:
-    """32-bit rows table[id] + pos_table[position]."""
+def embed_position(ids: torch.Tensor, positions: torch.Tensor | None, table: torch.Tensor,
+                   pos_table: torch.Tensor | None) -> torch.Tensor:
+    """32-bit rows table[id] + pos_table[position]; without a position table, table[id] alone."""
     _on_gpu(ids, positions, table, pos_table)
     tokens, (vocab, hidden) = ids.numel(), table.shape
-    assert ids.dtype == torch.int32 and positions.dtype == torch.int32 and positions.numel() == tokens
-    assert table.is_contiguous() and pos_table.is_contiguous() and pos_table.shape[1] == hidden
-    assert pos_table.dtype == table.dtype
+    assert ids.dtype == torch.int32 and table.is_contiguous()
+    if pos_table is not None:
+        assert positions.dtype == torch.int32 and positions.numel() == tokens
+        assert pos_table.is_contiguous() and pos_table.shape[1] == hidden and pos_table.dtype == table.dtype
     out = torch.empty((tokens, hidden), dtype=torch.float32, device=table.device)
     _check(lib("stream32").lab_embed_position(_ptr(out), _ptr(table), _ptr(pos_table), _ptr(ids),
-                                              _ptr(positions), tokens, hidden, vocab, pos_table.shape[0],
+                                              _ptr(positions if pos_table is not None else None), tokens, hidden,
+                                              vocab, pos_table.shape[0] if pos_table is not None else 0,
                                               dtype_code(table.dtype), _stream()), "embed_position")
     return out
 
 
 def stream_norm_add(x: torch.Tensor, a: torch.Tensor, weight: torch.Tensor, eps: float,
-                    bias: torch.Tensor | None = None, copy: bool = False) -> torch.Tensor | None:
+                    bias: torch.Tensor | None = None, copy: bool = False,
+                    next_weight: torch.Tensor | None = None) -> torch.Tensor | None:
     """x += rmsnorm(a + bias) * weight in place on the 32-bit stream; `a` is a 32-bit product [tokens, hidden]
     or split-K partial products [splits, tokens, hidden] (summed in ascending order).  With `copy`, returns
-    the new rows of x rounded to the weight's storage type."""
-    _on_gpu(x, a, weight, bias)
+    the new rows of x rounded to the weight's storage type; with `next_weight`, returns rmsnorm(new x) *
+    next_weight instead (the norm that opens the next sublayer), rounded likewise."""
+    _on_gpu(x, a, weight, bias, next_weight)
+    copy = copy or next_weight is not None
+    assert next_weight is None or (next_weight.dtype == weight.dtype and next_weight.numel() == x.shape[1])
     tokens, hidden = x.shape
     assert x.dtype == torch.float32 and x.is_contiguous() and a.dtype == torch.float32 and a.is_contiguous()
     assert a.shape[-2:] == x.shape and weight.numel() == hidden and (bias is None or bias.dtype == weight.dtype)
     splits = a.shape[0] if a.dim() == 3 else 1
     rounded = torch.empty((tokens, hidden), dtype=weight.dtype, device=x.device) if copy else None
     _check(lib("stream32").lab_stream_norm_add(_ptr(x), _ptr(rounded), _ptr(a), splits, _ptr(bias), _ptr(weight), tokens,
-                                               hidden, ctypes.c_float(eps), dtype_code(weight.dtype), _stream()),
+                                               hidden, ctypes.c_float(eps), _ptr(next_weight),
+                                               dtype_code(weight.dtype), _stream()),
            "stream_norm_add")
     return rounded
 
@@ -1302,3 +1329,161 @@ def gelu_tanh_(x: torch.Tensor) -> torch.Tensor:
     assert x.is_contiguous()
     _check(lib("rowwise").lab_gelu_tanh(_ptr(x), ctypes.c_longlong(x.numel()), dtype_code(x.dtype), _stream()), "gelu_tanh")
     return x
+
+
+# ----------------------------------------------------------------------------------------
+# Rotation of neighbouring pairs with the paged store (csrc/kernels/rope_pairs.cu).
+# ----------------------------------------------------------------------------------------
+def rope_pairs_store(proj: torch.Tensor, bias, positions: torch.Tensor, inv_freq: torch.Tensor, rot_dims: int, slots,
+                     cache_k, cache_v, n_q: int, n_kv: int, dim: int, vdim: int, head: int, k_at: int, v_at: int,
+                     dtype: torch.dtype) -> torch.Tensor:
+    """From the 32-bit projection of a step's rows (whole [tokens, width] or split-K partial products
+    [splits, tokens, width]; q heads first, key heads from column k_at, value heads from v_at, which may equal
+    k_at: the values are then the keys before their rotation): bias added, the first `rot_dims` entries of every
+    q and k head turned pair by pair (entries 2i and 2i + 1 by position * inv_freq[i]), q returned in `dtype`
+    [tokens, n_q * head] (zeros beyond `dim`), k and v written to the rows' slots (`slots` None: no write)."""
+    _on_gpu(proj, bias, positions, inv_freq, slots, cache_k, cache_v)
+    splits = proj.shape[0] if proj.dim() == 3 else 1
+    tokens, ld = proj.shape[-2], proj.shape[-1]
+    assert proj.dtype == torch.float32 and proj.is_contiguous()
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() >= rot_dims // 2
+    assert bias is None or bias.dtype == dtype
+    write = slots is not None
+    n_slots = page_size = 0
+    if write:
+        assert cache_k.shape == cache_v.shape and cache_k.shape[1] == n_kv and cache_k.shape[3] == head
+        assert cache_k.dtype == dtype and cache_k.is_contiguous() and cache_v.is_contiguous()
+        page_size = cache_k.shape[2]
+        n_slots = cache_k.shape[0] * page_size
+    q = torch.empty((tokens, n_q * head), dtype=dtype, device=proj.device)
+    _check(lib("rope_pairs").lab_rope_pairs_store(
+        _ptr(q), _ptr(cache_k if write else None), _ptr(cache_v if write else None), _ptr(proj), splits,
+        ctypes.c_longlong(tokens * ld), ld, k_at, v_at, _ptr(bias), _ptr(positions), _ptr(inv_freq), rot_dims,
+        _ptr(slots), ctypes.c_longlong(n_slots), tokens, n_q, n_kv, dim, vdim, head, max(page_size, 1),
+        dtype_code(dtype), _stream()), "rope_pairs_store")
+    return q
+
+
+# ----------------------------------------------------------------------------------------
+# Selective scan (csrc/kernels/selective_scan.cu).
+# ----------------------------------------------------------------------------------------
+SELECTIVE_SCAN_MAX_STATE = 256
+
+
+def conv_silu(proj: torch.Tensor, conv_at: int, channels: int, taps: int, w: torch.Tensor, b: torch.Tensor,
+              kept: torch.Tensor, ctx, write: bool = True):
+    """silu(causal convolution) of columns [conv_at, conv_at + channels) of the 32-bit `proj` over each request's
+    last `taps` inputs (w [channels, taps], the last column on the row itself; bias b); `kept`
+    [slots, taps - 1, channels] holds every request's last inputs between steps and is brought up to date when
+    `write`.  Returns (32-bit result, the same rounded to the weights' type: the same tensor in a 32-bit engine)."""
+    _on_gpu(proj, w, b, kept)
+    tokens = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and w.is_contiguous() and w.shape == (channels, taps)
+    assert kept.dtype == torch.float32 and kept.is_contiguous() and tuple(kept.shape[1:]) == (max(taps - 1, 0), channels)
+    out32 = torch.empty((tokens, channels), dtype=torch.float32, device=proj.device)
+    out_t = out32 if w.dtype == torch.float32 else torch.empty((tokens, channels), dtype=w.dtype, device=proj.device)
+    _check(lib("selective_scan").lab_conv_silu(
+        _ptr(out32), _ptr(None if out_t is out32 else out_t), _ptr(proj), proj.stride(0), conv_at, channels, taps,
+        _ptr(w), _ptr(b), _ptr(kept), _ptr(ctx.row_req), _ptr(ctx.q_start), _ptr(ctx.state_slot), tokens, ctx.n_requests,
+        kept.shape[0], int(write), dtype_code(w.dtype), _stream()), "conv_silu", 2 if write and taps > 1 else 1)
+    return out32, out_t
+
+
+def selective_scan(x: torch.Tensor, dt_pre: torch.Tensor, bc: torch.Tensor, b_at: int, c_at: int, z: torch.Tensor,
+                   a_log: torch.Tensor, skip: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, ctx,
+                   write: bool = True) -> torch.Tensor:
+    """The walk of a state-space mixer with a decay per channel and state entry: 32-bit x, dt_pre, z
+    [tokens, channels] (rows may be strided), B and C [tokens, N] at columns b_at and c_at of `bc`; a_log
+    [channels, N], skip and dt_bias [channels] in the storage type; state [slots, channels, N] 32-bit.  Returns
+    (sum_n S C + skip x) * silu(z) rounded to the storage type."""
+    _on_gpu(x, dt_pre, bc, z, a_log, skip, dt_bias, state)
+    tokens, channels = x.shape
+    N = a_log.shape[1]
+    for t in (x, dt_pre, bc, z):
+        assert t.dtype == torch.float32 and t.stride(1) == 1 and t.shape[0] == tokens
+    assert a_log.is_contiguous() and a_log.shape[0] == channels and skip.numel() == channels and dt_bias.numel() == channels
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (channels, N)
+    if N > SELECTIVE_SCAN_MAX_STATE:
+        raise KernelError(f"selective_scan: a state of {N} entries a channel exceeds {SELECTIVE_SCAN_MAX_STATE}")
+    out = torch.empty((tokens, channels), dtype=a_log.dtype, device=x.device)
+    _check(lib("selective_scan").lab_selective_scan(
+        _ptr(out), out.stride(0), _ptr(x), x.stride(0), _ptr(dt_pre), dt_pre.stride(0), _ptr(bc), bc.stride(0), b_at,
+        c_at, _ptr(z), z.stride(0), _ptr(a_log), _ptr(skip), _ptr(dt_bias), _ptr(state), _ptr(ctx.q_start),
+        _ptr(ctx.state_slot), ctx.n_requests, channels, N, state.shape[0], int(write), dtype_code(a_log.dtype),
+        _stream()), "selective_scan")
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# Routed feed-forward layers (csrc/kernels/moe.cu and the grouped products).
+# ----------------------------------------------------------------------------------------
+def moe_route(logits: torch.Tensor, experts: int, top: int, gate_col: int = -1):
+    """From 32-bit router logits [tokens, >= experts] (column `gate_col` >= 0: the logit of a shared expert's
+    gate): (chosen experts [tokens, top] int32, their weights [tokens, top], sigmoid of the gate's logit
+    [tokens] or None)."""
+    _on_gpu(logits)
+    tokens = logits.shape[0]
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= experts
+    chosen = torch.empty((tokens, top), dtype=torch.int32, device=logits.device)
+    weight = torch.empty((tokens, top), dtype=torch.float32, device=logits.device)
+    gate = torch.empty((tokens,), dtype=torch.float32, device=logits.device) if gate_col >= 0 else None
+    _check(lib("moe").lab_moe_route(_ptr(chosen), _ptr(weight), _ptr(gate), _ptr(logits), logits.stride(0), tokens,
+                                    experts, top, gate_col, _stream()), "moe_route")
+    return chosen, weight, gate
+
+
+def grouped_rows(pairs: int, experts: int, tile: int) -> int:
+    """Rows of the layout in which every expert's pairs start on a border of `tile` rows, whatever the choice."""
+    return -(-(pairs + experts * (tile - 1)) // tile) * tile
+
+
+def moe_align(chosen: torch.Tensor, experts: int, tile: int):
+    """The (token, choice) pairs laid out in rows grouped by expert: (row_src [rows] int32: the pair at each row
+    or -1, tile_group [rows / tile] int32: the expert of each tile or -1, pos_of [pairs] int32: each pair's row)."""
+    _on_gpu(chosen)
+    pairs = chosen.numel()
+    rows = grouped_rows(pairs, experts, tile)
+    row_src = torch.empty((rows,), dtype=torch.int32, device=chosen.device)
+    tile_group = torch.empty((rows // tile,), dtype=torch.int32, device=chosen.device)
+    pos_of = torch.empty((pairs,), dtype=torch.int32, device=chosen.device)
+    _check(lib("moe").lab_moe_align(_ptr(row_src), _ptr(tile_group), _ptr(pos_of), _ptr(chosen), pairs, experts, tile,
+                                    rows, _stream()), "moe_align")
+    return row_src, tile_group, pos_of
+
+
+def moe_combine(y: torch.Tensor, pos_of: torch.Tensor, weight: torch.Tensor, shared: torch.Tensor | None,
+                shared_gate: torch.Tensor | None) -> torch.Tensor:
+    """out[t] = sum_k weight[t, k] * y[pos_of[t, k]] (+ shared_gate[t] * shared[t]), 32-bit."""
+    _on_gpu(y, pos_of, weight, shared, shared_gate)
+    tokens, top = weight.shape
+    width = y.shape[1]
+    assert y.dtype == torch.float32 and y.is_contiguous() and weight.dtype == torch.float32
+    assert shared is None or (shared.dtype == torch.float32 and shared.is_contiguous() and shared.shape == (tokens, width))
+    out = torch.empty((tokens, width), dtype=torch.float32, device=y.device)
+    _check(lib("moe").lab_moe_combine(_ptr(out), _ptr(y), _ptr(pos_of), _ptr(weight), _ptr(shared), _ptr(shared_gate),
+                                      tokens, top, width, _stream()), "moe_combine")
+    return out
+
+
+def grouped_tile_rows() -> int:
+    """Rows of a tile of the grouped product on the ordinary units."""
+    return int(lib("gemm_plain").lab_gemm_plain_group_rows())
+
+
+def linear_grouped(x: torch.Tensor, w: torch.Tensor, row_src: torch.Tensor | None, row_div: int,
+                   tile_group: torch.Tensor, rows: int, gated: bool = False, out_f32: bool = False) -> torch.Tensor:
+    """Row r of the result is x[row_src[r] // row_div] (row_src None: x[r]) times the matrix w[tile_group[r // tile]]
+    transposed; w [groups, out, in], with `gated` [groups, 2 * out, in] (gate rows, then up rows) and the result
+    silu(gate) * up.  Rows of tiles whose group is -1 are left unwritten; rows whose source is -1 read zeros."""
+    _on_gpu(x, w, row_src, tile_group)
+    K = x.shape[1]
+    N = w.shape[1] // 2 if gated else w.shape[1]
+    assert w.is_contiguous() and w.dim() == 3 and w.shape[2] == K and w.dtype == x.dtype and x.stride(1) == 1
+    assert row_src is not None or x.shape[0] >= rows
+    odt = torch.float32 if (out_f32 or x.dtype == torch.float32) else x.dtype
+    out = torch.empty((rows, N), dtype=odt, device=x.device)
+    _check(lib("gemm_plain").lab_gemm_plain_grouped(
+        _ptr(out), _ptr(x), _ptr(w), rows, N, K, x.stride(0), out.stride(0), int(gated),
+        ctypes.c_longlong(w.shape[1] * K), _ptr(row_src), int(row_div), _ptr(tile_group), dtype_code(x.dtype),
+        int(out_f32), _stream()), "gemm_plain_grouped")
+    return out

@@ -69,6 +69,7 @@ class CachePlan:
     group_of: tuple[int, ...]               # cache id -> group index (-1: no paged group)
     group_windows: tuple[int, ...]          # per paged group: 0 or the window
     group_keys: tuple = ()                  # per paged group: the key its needs share
+    group_keeps: tuple = ()                 # per paged group: first positions a windowed group keeps for good
 
     def group_for(self, need: CacheNeed) -> int:
         """The paged group of a need (also of one part of a need made of parts); -1 if it is not paged."""
@@ -113,7 +114,8 @@ def cache_plan(bp: ModelBlueprint) -> CachePlan:
             if paged.group_key() not in keys:
                 keys.append(paged.group_key())
         group_of.append(keys.index(need.group_key()) if isinstance(need, (PagedKV, PagedLatent)) else -1)
-    return CachePlan(tuple(needs), tuple(block_needs), tuple(group_of), tuple(k[1] for k in keys), tuple(keys))
+    return CachePlan(tuple(needs), tuple(block_needs), tuple(group_of), tuple(k[1] for k in keys), tuple(keys),
+                     tuple(k[2] for k in keys))
 
 
 class CausalLM:

@@ -200,3 +200,73 @@ class NormedSublayersBlock(Block):
 
 
 register_part("block", "normed_sublayers_stream", NormedSublayersBlock)
+
+
+@dataclasses.dataclass
+class PendingNormedAdd:
+    """What a block whose sublayers' outputs are normed still owes a 32-bit stream: x += rmsnorm(a + bias) * weight,
+    `a` a 32-bit product or split-K partial products.  The norm that reads the stream next adds it in its own pass
+    (`add_norm`); whoever needs the stream itself first calls `add_to`."""
+    a: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+    bias: Optional[torch.Tensor] = None
+
+    def add_to(self, x):
+        ops.stream_norm_add(x, self.a, self.weight, self.eps, bias=self.bias)
+        return x
+
+    def add_norm(self, x, next_weight):
+        """x += what is owed; returns rmsnorm(x) * next_weight with the same eps, rounded to the storage type."""
+        return ops.stream_norm_add(x, self.a, self.weight, self.eps, bias=self.bias, next_weight=next_weight)
+
+
+class SandwichStreamBlock(Block):
+    """Every sublayer between two norms on a 32-bit residual stream:
+
+        x <- x + norm1b(mixer(norm1(x)));   x <- x + norm2b(ffn(norm2(x)))
+
+    (RMS norms with plain weights and one eps; a layer may have no feed-forward: two norms then.)  The
+    sublayers' products arrive in 32-bit, whole or as split-K partial products; one kernel sums them, norms
+    them, adds to the stream and, in the same pass, norms the new row for the sublayer that reads it next.
+    The last sum of a block is left to the norm that opens the next block (or to the final norm):
+    `PendingNormedAdd`."""
+    decode_graph_safe = True
+
+    n_norms = 4
+
+    @classmethod
+    def libraries(cls, spec, dtype):
+        return [("stream32", {})]
+
+    def __init__(self, mixer, ffn, norms, spec=None, weights=None, dtype=None, device=None):
+        super().__init__(mixer, ffn, norms, spec, weights, dtype, device)
+        want = 4 if ffn is not None else 2
+        if len(norms) < want:
+            raise ValueError(f"sandwich_stream: {want} norms (before and after each sublayer), got {len(norms)}")
+        for n in norms[:want]:
+            if type(n) is not StreamRMSNorm or n.offset != 0.0 or n.eps != norms[0].eps:
+                raise ValueError("sandwich_stream: the norms are rmsnorm_stream with plain weights and one eps")
+
+    def forward(self, x, pending, ctx, cache):
+        before, after = self.norms[0], self.norms[1]
+        with scoped_range(self.mixer_range):
+            if pending is not None and hasattr(pending, "add_norm") and pending.eps == before.eps:
+                h = pending.add_norm(x, before.weight)
+            else:
+                if pending is not None:
+                    if not hasattr(pending, "add_to"):
+                        raise ValueError("sandwich_stream follows a block whose sum it cannot take")
+                    pending.add_to(x)
+                h = ops.norm_stream(x, before.eps, 0.0, weight=before.weight)[1]
+            a = self.mixer.forward(h, ctx, cache)
+        if self.ffn is None:
+            return x, PendingNormedAdd(a, after.weight, after.eps)
+        before2, after2 = self.norms[2], self.norms[3]
+        with scoped_range(self.ffn_range):
+            h = ops.stream_norm_add(x, a, after.weight, after.eps, next_weight=before2.weight)
+            f = self.ffn.forward(h, ctx)
+        return x, PendingNormedAdd(f, after2.weight, after2.eps)
+
+
+register_part("block", "sandwich_stream", SandwichStreamBlock)

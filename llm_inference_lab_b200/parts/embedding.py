@@ -71,6 +71,27 @@ class TokenPositionEmbedding(Embedding):
         return ops.embed_position(token_ids, positions, self.table, self.positions)
 
 
+class StreamTokenEmbedding(Embedding):
+    """x[t] = table[id_t] as a 32-bit residual stream, no scaling, no positions."""
+
+    @classmethod
+    def tensors(cls, spec: PartSpec):
+        return [TensorSpec(spec["table"], (spec["vocab"], spec["hidden"]), init="table")]
+
+    @classmethod
+    def libraries(cls, spec, dtype):
+        return [("stream32", {})]
+
+    def __init__(self, spec, weights, dtype, device):
+        super().__init__(spec, weights, dtype, device)
+        t = weights[spec["table"]]
+        self.table = (t if t.dtype == dtype else t.to(dtype)).contiguous()
+        weights[spec["table"]] = self.table      # a tied head shares this storage
+
+    def forward(self, token_ids, positions=None):
+        return ops.embed_position(token_ids, None, self.table, None)
+
+
 class LinearHead(Head):
     """logits = x W^T in 32-bit, no bias; W is the embedding table when tied
     (rust/engine/src/runner/model/qwen2/engine.rs:299-303, 1312-1319)."""
@@ -104,4 +125,5 @@ class LinearHead(Head):
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("embedding", "normed_token_embedding", NormedTokenEmbedding)
 register_part("embedding", "token_position_embedding", TokenPositionEmbedding)
+register_part("embedding", "token_embedding_stream", StreamTokenEmbedding)
 register_part("head", "linear_head", LinearHead)

@@ -10,7 +10,8 @@ from .spec import PagedLatent, PartSpec, TensorSpec
 
 
 class LatentAttention(Mixer):
-    """Queries through a latent: c_q = rmsnorm(W_dq h), q = W_uq c_q, per head [dim plain ; rot_dim rotated].
+    """Queries through a latent: c_q = rmsnorm(W_dq h), q = W_uq c_q, per head [dim plain ; rot_dim rotated]
+    (`q_rank` 0: no query latent, q = W_q h directly, tensor `q`).
     Keys and values through another: W_dkv h gives kv_rank numbers, RMS-normed into the latent c, and
     rot_dim more, rotated, one key part shared by all heads.  Per head the plain key is W_uk c and the
     value W_uv c; score = (q_plain . k_plain + q_rot . k_rot) * scale.  Only [c ; k_rot] is cached, one
@@ -21,7 +22,9 @@ class LatentAttention(Mixer):
     is, for prompts' portions and decoded tokens alike.  Parameters: `window` (0: all keys; else a query at
     p sees the keys j with 0 <= p - j < window), `sink` (a learned number per head that joins the softmax's
     denominator, unscaled, without key or value), rotary base and the number of rotated entries `rot_dims`
-    of the rotated part (entry i pairs with i + rot_dims / 2), `scale`."""
+    of the rotated part (entry i pairs with i + rot_dims / 2; with `rot_pairs` entry 2i with 2i + 1), `scale`.
+    `own_kv` False: the layer has no W_dkv and reads the latents another layer call caches (its cache is the
+    other call's, not written here), with its own W_uk, W_uv and queries."""
     decode_graph_safe = True
 
 
@@ -29,10 +32,14 @@ class LatentAttention(Mixer):
     def tensors(cls, spec: PartSpec):
         h, H, D, R, V = spec["hidden"], spec["heads"], spec["dim"], spec["rot_dim"], spec["vdim"]
         Q, C, p = spec["q_rank"], spec["kv_rank"], spec.prefix
-        out = [TensorSpec(p + "dq", (Q, h)), TensorSpec(p + "dq.norm", (Q,), init="norm"),
-               TensorSpec(p + "uq", (H * (D + R), Q)), TensorSpec(p + "dkv", (C + R, h)),
-               TensorSpec(p + "dkv.norm", (C,), init="norm"), TensorSpec(p + "uk", (H * D, C)),
-               TensorSpec(p + "uv", (H * V, C)), TensorSpec(p + "o", (h, H * V))]
+        if Q:
+            out = [TensorSpec(p + "dq", (Q, h)), TensorSpec(p + "dq.norm", (Q,), init="norm"),
+                   TensorSpec(p + "uq", (H * (D + R), Q))]
+        else:
+            out = [TensorSpec(p + "q", (H * (D + R), h))]
+        if spec.get("own_kv", True):
+            out += [TensorSpec(p + "dkv", (C + R, h)), TensorSpec(p + "dkv.norm", (C,), init="norm")]
+        out += [TensorSpec(p + "uk", (H * D, C)), TensorSpec(p + "uv", (H * V, C)), TensorSpec(p + "o", (h, H * V))]
         if spec.get("sink"):
             out.append(TensorSpec(p + "sink", (H,), init="bias"))
         return out
@@ -61,9 +68,15 @@ class LatentAttention(Mixer):
         self.rot_dims = int(spec.get("rot_dims", self.rot_dim))
         if self.rot_dims % 2 or self.rot_dims > self.rot_dim:
             raise ValueError("latent_attention: rot_dims must be even and at most rot_dim")
+        self.own_kv, self.rot_pairs = bool(spec.get("own_kv", True)), bool(spec.get("rot_pairs"))
+        if self.q_rank and not self.own_kv:
+            raise ValueError("latent_attention: a layer that borrows its latents projects its queries directly (q_rank 0)")
         w = lambda n: self._weight(weights, n)  # noqa: E731
-        self.w_down = torch.cat([w("dq"), w("dkv")], dim=0).contiguous()
-        self.norm_q, self.norm_c = w("dq.norm"), w("dkv.norm")
+        # the matrices that read h and leave in 32-bit for the norms: the query's latent, then the keys' and values'
+        down = ([w("dq")] if self.q_rank else []) + ([w("dkv")] if self.own_kv else [])
+        self.w_down = torch.cat(down, dim=0).contiguous() if down else None
+        self.norm_q = w("dq.norm") if self.q_rank else None
+        self.norm_c = w("dkv.norm") if self.own_kv else None
         H, D, R, C, V = self.heads, self.dim, self.rot_dim, self.kv_rank, self.vdim
         # A head of q and of the heads' output is HD wide: the plain form's head size where it serves (keys
         # dim + rot_dim, values vdim, padded with zero rows and columns of the matrices around them), else
@@ -71,9 +84,10 @@ class LatentAttention(Mixer):
         self.plain_form = ops.latent_plain_form_supported(dtype, D, R, V) and self.PLAIN_FORM_ROWS > 0
         self.hd_q = ops.latent_head_size(D, R, V) if self.plain_form else D + R
         self.hd_o = self.hd_q if self.plain_form else V
-        w_uq = torch.zeros((H, self.hd_q, self.q_rank), dtype=dtype, device=w("uq").device)
-        w_uq[:, : D + R] = w("uq").view(H, D + R, self.q_rank)
-        self.w_uq = w_uq.view(H * self.hd_q, self.q_rank).contiguous()
+        w_q = w("uq") if self.q_rank else w("q")       # what forms q: from the query latent, or from h itself
+        w_uq = torch.zeros((H, self.hd_q, w_q.shape[1]), dtype=dtype, device=w_q.device)
+        w_uq[:, : D + R] = w_q.view(H, D + R, w_q.shape[1])
+        self.w_uq = w_uq.view(H * self.hd_q, w_q.shape[1]).contiguous()
         # per head: the key projection transposed (it meets the query), the value projection as stored
         self.w_uk_t = w("uk").view(H, D, C).transpose(1, 2).contiguous()      # [H, C, D]
         self.w_uv = w("uv").view(H, V, C).contiguous()                        # [H, V, C]
@@ -90,10 +104,15 @@ class LatentAttention(Mixer):
         group = ctx.groups[cache.group]
         H, D, R, C, V = self.heads, self.dim, self.rot_dim, self.kv_rank, self.vdim
         T = x.shape[0]
-        proj = ops.linear(x, self.w_down, None, out_f32=True)
-        write = cache.write
-        cq = ops.latent_prep(proj, self.q_rank, C, R, self.norm_q, self.norm_c, ctx.row_pos, self.inv_freq,
-                             self.rot_dims, group.row_slot if write else None, cache.k if write else None, self.eps)
+        write = cache.write and self.own_kv
+        cq = x
+        if self.w_down is not None:
+            proj = ops.linear(x, self.w_down, None, out_f32=True)
+            cq = ops.latent_prep(proj, self.q_rank, C, R, self.norm_q, self.norm_c, ctx.row_pos, self.inv_freq,
+                                 self.rot_dims, group.row_slot if write else None, cache.k if write else None,
+                                 self.eps, pairs=self.rot_pairs)
+            if not self.q_rank:
+                cq = x
         q = ops.linear(cq, self.w_uq, None)
         rows_plain = self.PLAIN_FORM_ROWS if self.plain_form else 0
         plain = rows_plain > 0 and any(n >= rows_plain for n in ctx.q_lens)
@@ -103,13 +122,15 @@ class LatentAttention(Mixer):
         attn = make((T, H * self.hd_o), dtype=self.dtype, device=x.device)
         if absorbed:
             q_cat = torch.empty((T, H, C + R), dtype=torch.float32, device=x.device)
-            ops.latent_q_rope(q, q_cat, H, D, R, C, ctx.row_pos, self.inv_freq, self.rot_dims, in_place=plain)
+            ops.latent_q_rope(q, q_cat, H, D, R, C, ctx.row_pos, self.inv_freq, self.rot_dims, in_place=plain,
+                              pairs=self.rot_pairs)
             ops.linear_heads(q.view(T, H, self.hd_q), self.w_uk_t, q_cat)
             mixed = ops.latent_attention(q_cat, cache.k, self.sink, ctx, group, H, C, self.window, self.scale,
                                          below=rows_plain if plain else 0)
             ops.linear_heads(mixed.view(T, H, C), self.w_uv, attn.view(T, H, self.hd_o))
         else:
-            ops.latent_q_rope(q, None, H, D, R, C, ctx.row_pos, self.inv_freq, self.rot_dims, in_place=True)
+            ops.latent_q_rope(q, None, H, D, R, C, ctx.row_pos, self.inv_freq, self.rot_dims, in_place=True,
+                              pairs=self.rot_pairs)
         if plain:
             ops.latent_attention_plain_form(q, cache.k, self.w_up, self.sink, ctx, group, H, D, R, V, C, self.window,
                                             self.scale, rows_plain, attn)

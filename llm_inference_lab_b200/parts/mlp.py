@@ -49,10 +49,10 @@ register_part("feed_forward", "gated_mlp", GatedMLP)
 
 class DenseMLP(FeedForward):
     """down( act(x Wu^T + bu) ) + bd: one matrix up, an activation, one matrix down, biases optional.  `act`
-    is "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).  The activation is the epilogue of
-    the up product where the product kernel has it."""
+    is "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))) or "relu2" (max(z, 0)^2).  The activation
+    is the epilogue of the up product where the product kernel has it."""
 
-    ACTS = ("gelu_tanh",)
+    ACTS = ("gelu_tanh", "relu2")
     NAMES = {"up": "up_proj.weight", "down": "down_proj.weight", "bias": ".bias"}
 
     @classmethod
@@ -78,15 +78,18 @@ class DenseMLP(FeedForward):
         self.b_up = self._weight(weights, n["up"] + n["bias"]) if spec.get("bias") else None
         self.b_down = self._weight(weights, n["down"] + n["bias"]) if spec.get("bias") else None
         self.out_f32 = bool(spec.get("out_f32"))
+        self.act = spec["act"]
 
     def forward(self, x, ctx):
-        act = ops.linear(x, self.w_up, self.b_up, act="gelu_tanh")
+        act = ops.linear(x, self.w_up, self.b_up, act=self.act)
+        if self.out_f32 and self.b_down is None:      # a 32-bit consumer sums partial products itself
+            return ops.linear(act, self.w_down, None, out_f32=True, allow_partial=True)
         return ops.linear(act, self.w_down, self.b_down, out_f32=self.out_f32)
 
     def forward_open(self, x, ctx):
         """(the down product without its bias, whole or as 32-bit split-K partial products; the bias or None):
         for a consumer that sums partial products and adds the bias in its own pass."""
-        act = ops.linear(x, self.w_up, self.b_up, act="gelu_tanh")
+        act = ops.linear(x, self.w_up, self.b_up, act=self.act)
         return ops.linear(act, self.w_down, None, out_f32=True, allow_partial=True), self.b_down
 
 

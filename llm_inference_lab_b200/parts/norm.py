@@ -46,6 +46,13 @@ class StreamRMSNorm(Norm):
         return ops.norm_stream(x, self.eps, self.offset, weight=self.weight, rows=rows)[1]
 
     def forward_add(self, x, delta, rows=None):
+        if delta is not None and hasattr(delta, "add_norm"):
+            # a normed product is owed (`parts.block.PendingNormedAdd`): with all rows wanted, added in this
+            # norm's pass; else added first
+            if rows is None and delta.eps == self.eps and self.offset == 0.0:
+                return delta.add_norm(x, self.weight)
+            delta.add_to(x)
+            return self.forward(x, rows)
         if delta is None or not hasattr(delta, "a"):      # nothing owed (or rows already rounded: `RoundedStream`)
             return self.forward(x, rows)
         # what the block before still owes the stream (`parts.block.PendingSum`): added here, in the norm's pass

@@ -93,14 +93,16 @@ class ModelBlueprint:
 
 @dataclasses.dataclass(frozen=True)
 class PagedKV:
-    """Keys and values for every position (window == 0) or for the last ``window`` ones."""
+    """Keys and values for every position (window == 0) or for the last ``window`` ones; with a window,
+    ``keep_first`` > 0 keeps the first that many positions readable for the request's whole life."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    keep_first: int = 0
 
     def group_key(self):
         # Layers whose pages live and die together share a block table.
-        return ("paged_kv", self.window)
+        return ("paged_kv", self.window, self.keep_first if self.window else 0)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -112,7 +114,7 @@ class PagedLatent:
     window: int = 0
 
     def group_key(self):
-        return ("paged_kv", self.window)
+        return ("paged_kv", self.window, 0)
 
 
 @dataclasses.dataclass(frozen=True)

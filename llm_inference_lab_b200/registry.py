@@ -70,6 +70,8 @@ def _register_builtin() -> None:
     register_architecture("Sogulix", SogulixConfig, sogulix_blueprint)
     from .config.ritizen import RitizenConfig, ritizen_blueprint
     register_architecture("Ritizen", RitizenConfig, ritizen_blueprint)
+    from .config.bukatar import BukatarConfig, bukatar_blueprint
+    register_architecture("Bukatar", BukatarConfig, bukatar_blueprint)
 
 
 _register_builtin()
