@@ -58,12 +58,13 @@ __device__ __forceinline__ long long key_offset(const int* __restrict__ bt, int 
 // One tile of BN keys for 16 query rows held by a warp: scores, masked online softmax, PV.
 //   qf: the rows' q fragments; ks/vs: shared-memory tiles [BN][ROW_BYTES];
 //   rows of this thread: lane/4 (index 0) and lane/4 + 8 (index 1); a key j is visible to row i
-//   iff lo[i] <= j <= hi[i].  m, l, o carry the running max (log2 units), sum and accumulator.
+//   iff j <= hi[i] and (lo[i] <= j or j < keep): `keep` first positions of the sequence stay visible
+//   before a window.  m, l, o carry the running max (log2 units), sum and accumulator.
 template <int BN>
 __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], uint32_t ks, uint32_t vs,
                                           float (&o)[DTILES][4], float (&m)[2], float (&l)[2], int key0,
                                           const int (&lo)[2], const int (&hi)[2], float scale_log2, int lane,
-                                          bool all_visible = false) {
+                                          bool all_visible = false, int keep = 0) {
   float s[BN / 8][4];
 #pragma unroll
   for (int j = 0; j < BN / 8; ++j)
@@ -90,7 +91,7 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], uint3
     for (int e = 0; e < 4; ++e) {
       const int key = key0 + j * 8 + 2 * (lane & 3) + (e & 1);
       const int r = e >> 1;
-      const bool ok = all_visible || (key >= lo[r] && key <= hi[r]);
+      const bool ok = all_visible || ((key >= lo[r] || key < keep) && key <= hi[r]);
       s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
       mx[r] = fmaxf(mx[r], s[j][e]);
     }
@@ -144,16 +145,18 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], uint3
 // R consecutive keys (R <= 32) and their values copied by one warp: lane r < R looks up the page
 // of key0 + r once, then the lanes share the row offsets by shuffle, so that a tile costs one
 // page lookup per lane and no 64-bit arithmetic per 16-byte chunk.  Keys outside
-// [first_key, kv_len) and keys whose page was given back become rows of zeros (they are masked).
+// [first_key, kv_len) that are not among the first `keep`, and keys whose page was given back, become
+// rows of zeros (they are masked).
 template <int R>
 __device__ __forceinline__ void load_kv_rows_warp(uint32_t dst_k, uint32_t dst_v,
                                                   const __nv_bfloat16* __restrict__ cache_k,
                                                   const __nv_bfloat16* __restrict__ cache_v,
                                                   const int* __restrict__ bt, int key0, int first_key, int kv_len,
-                                                  int kvh, int n_kv, int page_size, int num_pages, int lane) {
+                                                  int kvh, int n_kv, int page_size, int num_pages, int lane,
+                                                  int keep = 0) {
   const int j = key0 + lane;
   long long mine = -1;
-  if (lane < R && j >= first_key && j < kv_len) mine = key_offset(bt, j, kvh, n_kv, page_size, num_pages);
+  if (lane < R && (j >= first_key || j < keep) && j < kv_len) mine = key_offset(bt, j, kvh, n_kv, page_size, num_pages);
   if (mine == -2) lab_set_error(LAB_ERR_PAGE_RANGE);
   constexpr int CHUNKS = R * CPR;
   constexpr int PASSES = (CHUNKS + 31) / 32;

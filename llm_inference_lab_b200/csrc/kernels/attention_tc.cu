@@ -32,7 +32,7 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
     const __nv_bfloat16* __restrict__ cache_k, const __nv_bfloat16* __restrict__ cache_v,
     const int* __restrict__ q_start, const int* __restrict__ kv_len_arr, const int* __restrict__ pos0_arr,
     const int* __restrict__ block_table, int max_blocks, int n_q, int n_kv, int page_size, int num_pages, int window,
-    float scale_log2, int min_q_len, const float* __restrict__ sink) {
+    float scale_log2, int min_q_len, const float* __restrict__ sink, int keep) {
   extern __shared__ __align__(16) uint8_t smem[];
   pdl_trigger();
   pdl_wait();
@@ -62,15 +62,20 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
   const int hi_all = p0 + last_row;
   const int lo_all = lab_first_key(p0 + r0, window);
   const int t_first = lo_all / PF_BN, t_last = hi_all / PF_BN;
+  // Beside a window the first `keep` positions stay visible: their tiles, as far as they lie before the
+  // window's first tile, are walked first; step i of the walk meets tile tile_of(i).
+  const int n_kept = keep > 0 ? min(t_first, (keep + PF_BN - 1) / PF_BN) : 0;
+  const int n_steps = n_kept + t_last - t_first + 1;
+  auto tile_of = [&](int i) { return i < n_kept ? i : t_first + (i - n_kept); };
 
   auto issue = [&](int t, int stage) {
     const uint32_t kd = kv_s + stage * 2 * PF_TILE_BYTES;
     constexpr int RW = PF_BN / (PF_THREADS / 32);  // rows of the tile each warp copies
     load_kv_rows_warp<RW>(kd + warp * RW * ROW_BYTES, kd + PF_TILE_BYTES + warp * RW * ROW_BYTES, cache_k, cache_v, bt,
-                          t * PF_BN + warp * RW, lo_all, kvl, kvh, n_kv, page_size, num_pages, lane);
+                          t * PF_BN + warp * RW, lo_all, kvl, kvh, n_kv, page_size, num_pages, lane, keep);
     cp_async_commit();
   };
-  issue(t_first, 0);
+  issue(tile_of(0), 0);
 
   int lo[2], hi[2];
 #pragma unroll
@@ -95,10 +100,10 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
 
   uint32_t qf[KSTEPS][4];
   bool have_q = false;
-  for (int t = t_first; t <= t_last; ++t) {
-    const int stage = (t - t_first) & 1;
-    if (t + 1 <= t_last) {
-      issue(t + 1, stage ^ 1);
+  for (int i = 0; i < n_steps; ++i) {
+    const int stage = i & 1, t = tile_of(i);
+    if (i + 1 < n_steps) {
+      issue(tile_of(i + 1), stage ^ 1);
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
@@ -117,11 +122,13 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
     const int warp_hi = p0 + min(r0 + warp * 16 + 15, ql - 1);
     if (t * PF_BN <= warp_hi) {
       const uint32_t kd = kv_s + stage * 2 * PF_TILE_BYTES;
-      // A tile that lies wholly before the warp's first row (and inside every row's window) needs no mask.
+      // A tile that lies wholly before the warp's first row (and inside every row's window, or among the
+      // kept first positions) needs no mask.
       const int first_row = r0 + warp * 16;
       const bool all_visible = first_row + 15 < ql && t * PF_BN + PF_BN - 1 <= p0 + first_row &&
-                               (window == 0 || t * PF_BN >= lab_first_key(p0 + first_row + 15, window));
-      tile_step<PF_BN>(qf, kd, kd + PF_TILE_BYTES, o, m, l, t * PF_BN, lo, hi, scale_log2, lane, all_visible);
+                               (window == 0 || t * PF_BN >= lab_first_key(p0 + first_row + 15, window) ||
+                                t * PF_BN + PF_BN <= keep);
+      tile_step<PF_BN>(qf, kd, kd + PF_TILE_BYTES, o, m, l, t * PF_BN, lo, hi, scale_log2, lane, all_visible, keep);
     }
     __syncthreads();  // the stage is refilled by the next iteration's prefetch
   }
@@ -187,7 +194,7 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
     __nv_bfloat16* __restrict__ cache_k, __nv_bfloat16* __restrict__ cache_v,
     const int* __restrict__ q_start, const int* __restrict__ kv_len_arr, const int* __restrict__ block_table,
     int max_blocks, int n_q, int n_kv, int page_size, int num_pages, int window, float scale_log2, int splits,
-    float* __restrict__ part_acc, float* __restrict__ part_ml) {
+    float* __restrict__ part_acc, float* __restrict__ part_ml, int keep, const float* __restrict__ sink) {
   extern __shared__ __align__(16) uint8_t smem[];
   using L = DcLayout<CLUSTER>;
   pdl_trigger();
@@ -210,9 +217,12 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
   const int head0 = kvh * group + mt * 16;           // first query head of this CTA
   const int n_heads = min(16, group - mt * 16);      // valid rows
 
-  // keys of this split: whole 32-key tiles counted from the 32-aligned start
+  // keys of this split: whole 32-key tiles counted from the 32-aligned start; before them the tiles of the
+  // first `keep` positions, as far as they lie before the start (tile t begins at key key_of(t))
   const int start = (first / DC_BN) * DC_BN;
-  const int total_tiles = kvl > start ? (kvl - start + DC_BN - 1) / DC_BN : 0;
+  const int n_kept = keep > 0 ? min(start / DC_BN, (keep + DC_BN - 1) / DC_BN) : 0;
+  auto key_of = [&](int t) { return t < n_kept ? t * DC_BN : start + (t - n_kept) * DC_BN; };
+  const int total_tiles = n_kept + (kvl > start ? (kvl - start + DC_BN - 1) / DC_BN : 0);
   const int tiles_per_split = (total_tiles + splits - 1) / splits;
   const int tile_lo = split * tiles_per_split;
   const int tile_hi = min(total_tiles, tile_lo + tiles_per_split);
@@ -220,16 +230,16 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
   const uint32_t ring = smem_u32(smem) + warp * L::WARP_BYTES;
   auto issue = [&](int t, int stage) {
     const uint32_t kd = ring + stage * 2 * DC_TILE_BYTES;
-    const int key0 = start + t * DC_BN;
+    const int key0 = key_of(t);
     load_kv_rows_warp<DC_BN>(kd, kd + DC_TILE_BYTES, cache_k, cache_v, bt, key0, first, kvl, kvh, n_kv,
-                             page_size, num_pages, lane);
+                             page_size, num_pages, lane, keep);
   };
   // this warp's tiles: tile_lo + warp, + DC_WARPS, ...; the first copies start before anything else
   int t_issue = tile_lo + warp;
   int staged = 0;
   for (; staged < L::STAGES - 1; ++staged) {
     // a tile that reaches the newest key waits for the kernel that writes it
-    if (t_issue < tile_hi && start + (t_issue + 1) * DC_BN >= kvl) break;
+    if (t_issue < tile_hi && key_of(t_issue) + DC_BN >= kvl) break;
     if (t_issue < tile_hi) issue(t_issue, staged);
     cp_async_commit();
     t_issue += DC_WARPS;
@@ -263,6 +273,19 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[t][e] = 0.f;
   const int lo[2] = {first, first}, hi[2] = {kvl - 1, kvl - 1};
+  if (sink != nullptr && split == 0 && warp == 0) {
+    // A sink: a number per query head that joins the softmax's denominator as exp(sink), unscaled, with no
+    // key and no value.  It opens the state of one warp of one split (running maximum in the scores' log2
+    // units, sum 1 in the lane that holds the row's sum) and reaches the result through the merges.
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = (lane >> 2) + 8 * r;
+      if (row < n_heads) {
+        m[r] = sink[head0 + row] * LOG2E;
+        l[r] = (lane & 3) == 0 ? 1.f : 0.f;
+      }
+    }
+  }
 
   int stage = 0;
   for (int t = tile_lo + warp; t < tile_hi; t += DC_WARPS) {
@@ -274,10 +297,10 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
     cp_async_wait<L::STAGES - 1>();
     __syncwarp();
     const uint32_t kd = ring + stage * 2 * DC_TILE_BYTES;
-    const int key0 = start + t * DC_BN;
+    const int key0 = key_of(t);
     // every key of an inner tile is visible to the one query row: no mask to evaluate
     tile_step<DC_BN>(qf, kd, kd + DC_TILE_BYTES, o, m, l, key0, lo, hi, scale_log2, lane,
-                     key0 >= first && key0 + DC_BN <= kvl);
+                     (key0 >= first || key0 + DC_BN <= keep) && key0 + DC_BN <= kvl, keep);
     __syncwarp();
     stage = (stage + 1) % L::STAGES;
   }
@@ -425,7 +448,7 @@ LAB_EXPORT int lab_attention_prefill(void* out, int out_stride, const void* q, i
                                      const void* cache_v, const int* q_start, const int* kv_len, const int* pos0,
                                      const int* block_table, int max_blocks, int requests, int max_q_len, int n_q,
                                      int n_kv, int page_size, int num_pages, int window, float scale, int min_q_len,
-                                     const float* sink, cudaStream_t stream) {
+                                     const float* sink, int keep_first, cudaStream_t stream) {
   if (requests <= 0 || max_q_len <= 0) return 0;
   if (n_q % n_kv || q_stride % 8 || (((uintptr_t)q) & 15)) return (int)cudaErrorInvalidValue;
   static bool configured = false;
@@ -439,14 +462,16 @@ LAB_EXPORT int lab_attention_prefill(void* out, int out_stride, const void* q, i
                          (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
                          (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v, q_start, kv_len, pos0,
                          block_table, max_blocks, n_q, n_kv, page_size, num_pages, window, scale * LOG2E, min_q_len,
-                         sink);
+                         sink, window > 0 && keep_first > 0 ? keep_first : 0);
 }
 
 static int decode_launch(void* out, int out_stride, const void* q, int q_stride, const void* cache_k,
                          const void* cache_v, const int* q_start, const int* kv_len, const int* block_table,
                          int max_blocks, int requests, int n_q, int n_kv, int page_size, int num_pages, int window,
-                         float scale, int splits, float* scratch, bool may_cluster, cudaStream_t stream) {
+                         float scale, int splits, float* scratch, bool may_cluster, cudaStream_t stream,
+                         int keep_first = 0, const float* sink = nullptr) {
   if (requests <= 0) return 0;
+  const int keep = window > 0 && keep_first > 0 ? keep_first : 0;
   const bool cluster = may_cluster && splits >= 2 && splits <= DC_MAX_CLUSTER;
   if (n_kv <= 0 || n_q % n_kv || splits < 1 || (splits > 1 && !cluster && scratch == nullptr)) return (int)cudaErrorInvalidValue;
   // The shared-memory limit is an attribute of the kernel on one device: set once per device.
@@ -482,7 +507,7 @@ static int decode_launch(void* out, int out_stride, const void* q, int q_stride,
     return (int)cudaLaunchKernelEx(&cfg, attention_decode_kernel<true>, (__nv_bfloat16*)out, out_stride,
                                    (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)cache_k, (__nv_bfloat16*)cache_v,
                                    q_start, kv_len, block_table, max_blocks, n_q, n_kv, page_size, num_pages, window,
-                                   scale * LOG2E, splits, (float*)nullptr, (float*)nullptr);
+                                   scale * LOG2E, splits, (float*)nullptr, (float*)nullptr, keep, sink);
   }
   float* part_acc = scratch;
   float* part_ml = scratch ? scratch + (size_t)requests * n_q * splits * D : nullptr;
@@ -490,7 +515,7 @@ static int decode_launch(void* out, int out_stride, const void* q, int q_stride,
                              (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
                              (__nv_bfloat16*)cache_k, (__nv_bfloat16*)cache_v, q_start, kv_len, block_table,
                              max_blocks, n_q, n_kv, page_size, num_pages, window, scale * LOG2E, splits, part_acc,
-                             part_ml);
+                             part_ml, keep, sink);
   if (e != cudaSuccess) return (int)e;
   if (splits > 1)
     e = lab_launch(attention_merge_kernel, dim3(requests, n_q), dim3(D), 0, stream, (__nv_bfloat16*)out, out_stride,
@@ -501,14 +526,16 @@ static int decode_launch(void* out, int out_stride, const void* q, int q_stride,
 // cluster_merge != 0 and 2 <= splits <= 8: the splits merge inside the kernel, through their cluster's
 // shared memory (worth it while all CTAs of the launch are resident at once); else the merge kernel
 // does it, from scratch: lab_attention_decode_scratch_floats(...) floats (may be null when unused).
+// keep_first: beside a window, the first that many positions stay visible; sink: null or a number per
+// query head that joins the softmax's denominator as exp(sink).
 LAB_EXPORT int lab_attention_decode(void* out, int out_stride, const void* q, int q_stride, const void* cache_k,
                                     const void* cache_v, const int* q_start, const int* kv_len,
                                     const int* block_table, int max_blocks, int requests, int n_q, int n_kv,
                                     int page_size, int num_pages, int window, float scale, int splits, float* scratch,
-                                    int cluster_merge, cudaStream_t stream) {
+                                    int cluster_merge, int keep_first, const float* sink, cudaStream_t stream) {
   return decode_launch(out, out_stride, q, q_stride, cache_k, cache_v, q_start, kv_len, block_table, max_blocks,
                        requests, n_q, n_kv, page_size, num_pages, window, scale, splits, scratch, cluster_merge != 0,
-                       stream);
+                       stream, keep_first, sink);
 }
 
 // ----------------------------------------------------------------------------------------

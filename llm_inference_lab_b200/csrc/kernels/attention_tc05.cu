@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
     const __nv_bfloat16* __restrict__ cache_k, const __nv_bfloat16* __restrict__ cache_v,
     const int* __restrict__ q_start, const int* __restrict__ kv_len_arr, const int* __restrict__ pos0_arr,
     const int* __restrict__ block_table, int max_blocks, int n_q, int n_kv, int page_size, int num_pages, int window,
-    float scale_log2, int min_q_len) {
+    float scale_log2, int min_q_len, int keep, const float* __restrict__ sink) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   Barriers* bar = reinterpret_cast<Barriers*>(smem + OFF_BAR);
@@ -107,7 +107,11 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
   const int hi_all = p0 + last_row;                                    // last key any row sees
   const int lo_all = lab_first_key(p0 + r0, window);                  // first key any row sees
   const int t_first = lo_all / BN, t_last = hi_all / BN;
-  const int n_tiles = t_last - t_first + 1;
+  // Beside a window the first `keep` positions stay visible: their tiles, as far as they lie before the
+  // window's first tile, are walked first; step j of the walk meets tile tile_of(j).
+  const int n_kept = keep > 0 ? min(t_first, (keep + BN - 1) / BN) : 0;
+  const int n_tiles = n_kept + t_last - t_first + 1;
+  auto tile_of = [&](int j) { return j < n_kept ? j : t_first + (j - n_kept); };
 
   if (threadIdx.x == 0) {
     mbar_init(&bar->q_full, 1);
@@ -152,8 +156,8 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
       kind = 0;
       page = -1;
       if (j < n_tiles && lane < pages_per_tile) {
-        const int k_lo = (t_first + j) * BN + lane * page_size;
-        if (k_lo < kvl && k_lo + page_size > lo_all) {
+        const int k_lo = tile_of(j) * BN + lane * page_size;
+        if (k_lo < kvl && (k_lo + page_size > lo_all || k_lo < keep)) {
           kind = k_lo + page_size > kvl ? 2 : 1;
           page = bt[k_lo / page_size];
         }
@@ -164,7 +168,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
     for (int j = 0; j < n_tiles && alive; ++j) {
       const int s = j % KV_STAGES;
       const uint32_t ph = (j / KV_STAGES) & 1;
-      const int key0 = (t_first + j) * BN;
+      const int key0 = tile_of(j) * BN;
       int kind = next_kind, page = next_page;
       classify(j + 1, next_kind, next_page);
       if (kind != 0 && (page < 0 || page >= num_pages)) {  // a page inside the length and the window must exist
@@ -294,7 +298,10 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
       // rounded to bfloat16 as ever, and O and l are 32-bit.  P overwrites the scores it came from.
       constexpr float RESCALE = 8.f;
       const uint32_t o_addr = lane_addr + TM_O;
-      float m_ref = -INFINITY, l = 0.f;
+      // A sink (a number per query head that joins the denominator as exp(sink), with no key and no value)
+      // opens the reference maximum; its share of the sum follows once the first tile's maximum is known.
+      const float m_sink = sink != nullptr ? sink[h] * LOG2E : -INFINITY;
+      float m_ref = m_sink, l = 0.f;
       bool ok = true;
       for (int j = 0; j < n_tiles; ++j) {
         const int sb = j & 1;
@@ -306,8 +313,8 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
 #pragma unroll
         for (int c = 0; c < BN / 32; ++c) tmem_ld32_issue(lane_addr + TM_S + sb * BN + c * 32, sr + c * 32);
         tmem_wait();
-        const int key0 = (t_first + j) * BN;
-        const bool all_visible = key0 >= lo && key0 + BN - 1 <= hi;
+        const int key0 = tile_of(j) * BN;
+        const bool all_visible = (key0 >= lo || key0 + BN <= keep) && key0 + BN - 1 <= hi;
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
         if (all_visible) {
 #pragma unroll
@@ -315,13 +322,14 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
         } else {
 #pragma unroll
           for (int c = 0; c < BN; ++c) {
-            if (key0 + c < lo || key0 + c > hi) sr[c] = __float_as_uint(-INFINITY);
+            if ((key0 + c < lo && key0 + c >= keep) || key0 + c > hi) sr[c] = __float_as_uint(-INFINITY);
             mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[c]));
           }
         }
         const float m_new = fmaxf(m_ref, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2);
         if (j == 0) {
           m_ref = m_new;
+          l = m_sink == -INFINITY ? 0.f : fast_exp2(m_sink - m_new);
         } else if (__any_sync(0xffffffffu, m_new > m_ref + RESCALE || (m_ref == -INFINITY && m_new != -INFINITY))) {
           // Some row of this warp has outgrown its reference: every row of the warp moves to its true
           // maximum.  The product of the previous tile must have landed in O before O is rescaled.
@@ -429,11 +437,14 @@ LAB_EXPORT int lab_attention_tc05_supports(int page_size) {
 }
 
 // Arguments as lab_attention_prefill; total_rows is the number of rows of q (for the TMA bounds).
+// keep_first: beside a window, the first that many positions stay visible; sink: null or a number per
+// query head that joins the softmax's denominator as exp(sink).
 LAB_EXPORT int lab_attention_prefill_tc05(void* out, int out_stride, const void* q, int q_stride, int total_rows,
                                           const void* cache_k, const void* cache_v, const int* q_start,
                                           const int* kv_len, const int* pos0, const int* block_table, int max_blocks,
                                           int requests, int max_q_len, int n_q, int n_kv, int page_size, int num_pages,
-                                          int window, float scale, int min_q_len, cudaStream_t stream) {
+                                          int window, float scale, int min_q_len, int keep_first, const float* sink,
+                                          cudaStream_t stream) {
   if (requests <= 0 || max_q_len <= 0) return 0;
   if (!lab_attention_tc05_supports(page_size) || n_q % n_kv || q_stride % 8 || (((uintptr_t)q) & 15) ||
       (((uintptr_t)cache_k) & 15) || (((uintptr_t)cache_v) & 15))
@@ -455,5 +466,5 @@ LAB_EXPORT int lab_attention_prefill_tc05(void* out, int out_stride, const void*
   return (int)lab_launch(attention_prefill_tc05_kernel, grid, dim3(THREADS), (size_t)SMEM, stream, mq, mk, mv,
                          (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v,
                          q_start, kv_len, pos0, block_table, max_blocks, n_q, n_kv, page_size, num_pages, window,
-                         scale * LOG2E, min_q_len);
+                         scale * LOG2E, min_q_len, window > 0 && keep_first > 0 ? keep_first : 0, sink);
 }

@@ -709,10 +709,14 @@ def decode_splits(n_decode: int, n_kv: int, group: int, max_kv_len: int, keys_pe
 
 
 def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requests, q_lens, max_kv_len,
-                 n_q, n_kv, head_dim, window, scale, out=None, splits=None, scratch=None):
+                 n_q, n_kv, head_dim, window, scale, out=None, splits=None, scratch=None, keep_first=0, sink=None):
     """Tensor-core attention: the prefill kernel serves requests with several new tokens,
-    the split-KV decode kernel those with one.  A negative `window` means chunks of that many positions."""
-    _on_gpu(q, cache_k, cache_v, q_start, kv_len, pos0, block_table)
+    the split-KV decode kernel those with one.  A negative `window` means chunks of that many positions.
+    `keep_first`: beside a window, the first that many positions stay visible.  `sink`: 32-bit numbers, one per
+    query head, that join the softmax's denominator as exp(sink) (a key with that unscaled score and no value)."""
+    _on_gpu(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, sink)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() >= n_q and sink.is_contiguous())
+    keep_first = int(keep_first) if window > 0 else 0
     if q.dtype != torch.bfloat16 or not attention_tc_supported(head_dim):
         raise KernelError(f"attention_tc: bfloat16 and a head size multiple of 16 up to 128, got {q.dtype}, {head_dim}")
     tokens = q.shape[0]
@@ -732,15 +736,17 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
         _check(L5.lab_attention_prefill_tc05(
             _ptr(out), out.stride(0), _ptr(q), q.stride(0), tokens, _ptr(cache_k), _ptr(cache_v), _ptr(q_start),
             _ptr(kv_len), _ptr(pos0), _ptr(block_table), block_table.shape[1], n_requests, max_q, n_q, n_kv,
-            page_size, num_pages, window, ctypes.c_float(scale), 2, _stream()), "attention_prefill_tc05")
+            page_size, num_pages, window, ctypes.c_float(scale), 2, keep_first, _ptr(sink), _stream()),
+            "attention_prefill_tc05")
     elif max_q > 1:
         _check(L.lab_attention_prefill(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_k), _ptr(cache_v),
                                        _ptr(q_start), _ptr(kv_len), _ptr(pos0), _ptr(block_table),
                                        block_table.shape[1], n_requests, max_q, n_q, n_kv, page_size, num_pages,
-                                       window, ctypes.c_float(scale), 2, None, _stream()), "attention_prefill")
+                                       window, ctypes.c_float(scale), 2, _ptr(sink), keep_first, _stream()),
+               "attention_prefill")
     if n_decode:
         if splits is None:
-            span = min(max_kv_len, abs(window)) if window else max_kv_len     # a chunk reaches as far as a window
+            span = min(max_kv_len, abs(window) + keep_first) if window else max_kv_len     # a chunk reaches as far as a window
             splits = decode_splits(n_decode, n_kv, n_q // n_kv, span, *decode_shape(head_dim))
         ctas = n_decode * n_kv * (-(-(n_q // n_kv) // 16)) * splits
         in_cluster = CLUSTER_MERGE and 2 <= splits <= 8 and ctas <= sm_count()
@@ -753,7 +759,8 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
         _check(L.lab_attention_decode(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_k), _ptr(cache_v),
                                       _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.shape[1],
                                       n_requests, n_q, n_kv, page_size, num_pages, window, ctypes.c_float(scale),
-                                      splits, _ptr(scratch), 1 if in_cluster else 0, _stream()), "attention_decode",
+                                      splits, _ptr(scratch), 1 if in_cluster else 0, keep_first, _ptr(sink), _stream()),
+               "attention_decode",
                2 if splits > 1 and not in_cluster else 1)
     return out
 
@@ -771,15 +778,25 @@ def attention(q, cache_k, cache_v, ctx, group, n_q, n_kv, head_dim, window, scal
         window = -int(chunk)
     if keep_first and window <= 0:
         keep_first = 0          # kept first positions only matter beside a window
-    if keep_first or sink_one:
-        # the first positions a window keeps, and the denominator's extra one, are the plain kernel's
-        return attention_plain(q, cache_k, cache_v, ctx.row_req, ctx.row_pos, group.block_table, n_q, n_kv, head_dim,
-                               window, scale, keep_first=keep_first, sink_one=sink_one)
     if q.dtype == torch.bfloat16 and not _force_plain and attention_tc_supported(head_dim):
+        # the denominator's extra one is a sink of 0 for every head
         return attention_tc(q, cache_k, cache_v, ctx.q_start, ctx.kv_len, ctx.pos0, group.block_table,
-                            ctx.n_requests, ctx.q_lens, ctx.max_kv_len, n_q, n_kv, head_dim, window, scale)
+                            ctx.n_requests, ctx.q_lens, ctx.max_kv_len, n_q, n_kv, head_dim, window, scale,
+                            keep_first=keep_first, sink=_zero_sinks(q.device, n_q) if sink_one else None)
     return attention_plain(q, cache_k, cache_v, ctx.row_req, ctx.row_pos, group.block_table, n_q, n_kv, head_dim,
-                           window, scale)
+                           window, scale, keep_first=keep_first, sink_one=sink_one)
+
+
+_zero_sink_cache: dict = {}
+
+
+def _zero_sinks(device, n_q: int) -> torch.Tensor:
+    """Zeros, one per query head (kept: a CUDA graph captured earlier still reads them)."""
+    key = (str(device), n_q)
+    t = _zero_sink_cache.get(key)
+    if t is None:
+        t = _zero_sink_cache[key] = torch.zeros((n_q,), dtype=torch.float32, device=device)
+    return t
 
 
 # ----------------------------------------------------------------------------------------
@@ -1097,7 +1114,7 @@ def latent_attention_plain_form(q: torch.Tensor, cache: torch.Tensor, w_up: torc
     _check(LA.lab_attention_prefill(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(pools[0]), _ptr(pools[1]),
                                     _ptr(ctx.q_start), _ptr(ctx.kv_len), _ptr(ctx.pos0), _ptr(table), table.shape[1],
                                     ctx.n_requests, ctx.max_q_len, heads, heads, page_size, num_pages, window,
-                                    ctypes.c_float(scale), int(at_least), _ptr(sink), _stream()), "attention_prefill")
+                                    ctypes.c_float(scale), int(at_least), _ptr(sink), 0, _stream()), "attention_prefill")
     return out
 
 

@@ -46,7 +46,15 @@ class PairRopeAttention(Mixer):
 
     @classmethod
     def libraries(cls, spec, dtype):
-        return [("rope_pairs", {}), ("attention_plain", {})]
+        out = [("rope_pairs", {})]
+        head = ops.padded_head(spec["dim"], spec["vdim"])
+        if dtype == torch.bfloat16 and ops.attention_tc_supported(head):
+            out.append(("attention_tc", {"LAB_HEAD_DIM": head}))
+            if head in (64, 128):
+                out.append(("attention_tc05", {"LAB_HEAD_DIM": head}))
+        else:
+            out.append(("attention_plain", {}))
+        return out
 
     def __init__(self, spec, weights, dtype, device):
         super().__init__(spec, weights, dtype, device)

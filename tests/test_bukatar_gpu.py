@@ -214,6 +214,98 @@ def test_window_edges_kept_tokens_and_the_extra_one(decode):
     ops.take_device_errors()
 
 
+def _fill_pages(ck, cv, table, r, k, v, page):
+    """Keys and values k, v [L, G, D] of request r into its pages."""
+    L = k.shape[0]
+    for b in range(-(-L // page)):
+        n = min(page, L - b * page)
+        ck[table[r, b], :, :n] = k[b * page: b * page + n].transpose(0, 1)
+        cv[table[r, b], :, :n] = v[b * page: b * page + n].transpose(0, 1)
+
+
+@pytest.mark.parametrize("D,H,G,page,window,keep,sink,prefill,cluster", [
+    (64, 4, 2, 16, 150, 70, True, "auto", True), (64, 4, 2, 16, 150, 70, True, "mma", False),
+    (128, 3, 1, 32, 40, 200, True, "auto", True), (64, 2, 2, 8, 300, 1, False, "auto", False),
+    (32, 6, 3, 16, 33, 64, True, "auto", True), (128, 2, 1, 64, 1000, 129, True, "auto", False),
+    (64, 20, 1, 16, 0, 0, True, "auto", True), (48, 2, 1, 16, 64, 65, False, "mma", True)])
+def test_tensor_core_attention_with_kept_first_tokens_and_the_extra_one(D, H, G, page, window, keep, sink, prefill,
+                                                                      cluster):
+    """The tensor-core attention kernels (tcgen05 prefill for long portions of heads of 64 and 128, mma.sync
+    prefill, split-key decode merged in a cluster or by the merge kernel) with a window, kept first tokens that
+    span several tiles, and the denominator's extra one, on shuffled pages: long and short portions beside single
+    tokens near and far from the start."""
+    torch = _torch()
+    from llm_inference_lab_b200.kernels import ops
+    rng = np.random.default_rng(D + window + keep)
+    q_lens, pos0 = [200, 1, 70, 1, 1, 3], [300, 900, 0, 40, 2500, 127]
+    pages = sum(-(-(n + p) // page) for n, p in zip(q_lens, pos0)) + 5
+    ctx, table = make_ctx(q_lens, pos0, list(range(len(q_lens))), page_size=page, num_pages=pages,
+                          shuffle=rng.permutation(pages))
+    dtype = torch.bfloat16
+    ck = torch.full((pages, G, page, D), float("nan"), dtype=dtype, device="cuda")
+    cv = torch.full_like(ck, float("nan"))
+    keys, vals = [], []
+    for r, (n, p0) in enumerate(zip(q_lens, pos0)):
+        k, v = _t(rng.standard_normal((p0 + n, G, D)), dtype), _t(rng.standard_normal((p0 + n, G, D)), dtype)
+        keys.append(_np(k)); vals.append(_np(v))
+        _fill_pages(ck, cv, table, r, k, v, page)
+    ck, cv = torch.nan_to_num(ck, nan=0.0), torch.nan_to_num(cv, nan=0.0)      # rows past a request's length
+    q = _t(rng.standard_normal((sum(q_lens), H * D)), dtype)
+    scale = 2.0 * D ** -0.5
+    old = ops.PREFILL_KERNEL, ops.CLUSTER_MERGE
+    ops.PREFILL_KERNEL, ops.CLUSTER_MERGE = prefill, cluster
+    try:
+        launches = ops.COUNTER.launches
+        got = _np(ops.attention(q, ck, cv, ctx, ctx.groups[0], H, G, D, window, scale, keep_first=keep, sink_one=sink))
+        assert ops.COUNTER.launches - launches >= 2        # a prefill kernel and a decode kernel, not the plain one
+    finally:
+        ops.PREFILL_KERNEL, ops.CLUSTER_MERGE = old
+    at = 0
+    for r, (n, p0) in enumerate(zip(q_lens, pos0)):
+        want = _plain_attention(_np(q[at: at + n]).reshape(n, H, D), keys[r], vals[r], range(p0, p0 + n), scale, window,
+                                keep, sink)
+        err = np.abs(got[at: at + n].reshape(n, H, D) - want).max()
+        assert err < 0.03, (r, err)
+        at += n
+    ops.take_device_errors()
+
+
+@pytest.mark.parametrize("n", [1, 6, 140])
+@pytest.mark.parametrize("D,page,window,keep", [(64, 16, 150, 70), (128, 32, 260, 130), (64, 8, 64, 64)])
+def test_tensor_core_window_edges_and_kept_tokens(n, D, page, window, keep):
+    """One key made to stand out in bfloat16 on the tensor-core kernels: the last row's output is its value while
+    the key is the window's last place or one of the kept first tokens, and not one place further; at tile and
+    page borders; for a single token, a short portion and a portion of more than one tile of rows."""
+    torch = _torch()
+    from llm_inference_lab_b200.kernels import ops
+    H, G, L = 2, 1, 1000
+    dtype = torch.bfloat16
+    for target, seen in ((L - 1, True), (L - window, True), (L - window - 1, False), (keep - 1, True), (keep, False),
+                         (0, True), (63, True), (64, keep > 64), (127, keep > 127), (128, keep > 128),
+                         (L - window + 1, True), (L - window - page, False), (500, L - 500 <= window)):
+        rng = np.random.default_rng(target)
+        pages = -(-L // page) + 3
+        ctx, table = make_ctx([n], [L - n], [0], page_size=page, num_pages=pages, shuffle=rng.permutation(pages))
+        k = 0.05 * rng.standard_normal((L, G, D))
+        v = rng.standard_normal((L, G, D))
+        k[target, 0, 3] = 40.0
+        q = np.zeros((n, H, D))
+        q[:, :, 3] = 1.0
+        ck = torch.zeros((pages, G, page, D), dtype=dtype, device="cuda")
+        cv = torch.zeros_like(ck)
+        _fill_pages(ck, cv, table, 0, _t(k, dtype), _t(v, dtype), page)
+        got = _np(ops.attention(_t(q.reshape(n, -1), dtype), ck, cv, ctx, ctx.groups[0], H, G, D, window, 1.0,
+                                keep_first=keep, sink_one=True))[-1].reshape(H, D)
+        v_t = _np(_t(v[target, 0], dtype))
+        if seen:
+            assert np.abs(got - v_t).max() < 0.02, target
+        else:
+            want = _plain_attention(_np(_t(q[-1:], dtype)), _np(_t(k, dtype)), _np(_t(v, dtype)), [L - 1], 1.0, window,
+                                    keep, True)[0]
+            assert np.abs(got - want).max() < 0.02 and np.abs(got - v_t).max() > 0.1, target
+    ops.take_device_errors()
+
+
 @pytest.mark.parametrize("channels,N,taps", [(16, 8, 4), (40, 5, 2), (24, 12, 1), (50, 40, 5), (32, 64, 3), (8, 70, 4)])
 def test_selective_scan_against_plain(channels, N, taps):
     """The convolution with kept inputs and the walk, against the plain recurrence: a whole sequence, portions
