@@ -770,6 +770,204 @@ def run_arch_ritizen(args):
     return 0
 
 
+# ----------------------------------------------------------------------------------------
+# --arch bukatar: the Bukatar design beside Ritizen and Qwen2 at equal layer sizes (random weights)
+# ----------------------------------------------------------------------------------------
+BUKATAR_SHAPES = {
+    # width, feed-forward and vocabulary of the Qwen2.5 shape of the same name; attention heads as there; the
+    # state-space mixer with inner = 2 x width; experts sized so that a token's share (top experts and the
+    # shared one) has the dense feed-forward's rows
+    "0.5B": dict(heads=14, kv_heads=2, dim=64, window=1024, keep_first=64, lat_dim=64, lat_rot=32, lat_vdim=64,
+                 kv_rank=256, inner=1792, state=16, dt_rank=56, taps=4, experts=8, top=2, expert_ff=1536,
+                 shared_ff=1792),
+    "1.5B": dict(heads=12, kv_heads=2, dim=128, window=2048, keep_first=128, lat_dim=96, lat_rot=32, lat_vdim=128,
+                 kv_rank=512, inner=3072, state=16, dt_rank=96, taps=4, experts=8, top=2, expert_ff=2816,
+                 shared_ff=3328),
+}
+
+
+def bukatar_config(shape, layers):
+    """Layers in the order state-space, windowed attention, latent attention, latent attention on the third one's
+    latents; dense and routed feed-forwards alternate."""
+    q, m = SHAPES[shape], BUKATAR_SHAPES[shape]
+    dense = {"kind": "dense", "ff": q["intermediate_size"]}
+    moe = {"kind": "moe", "router": {"experts": m["experts"], "top": m["top"]}, "expert": {"ff": m["expert_ff"]},
+           "shared": {"ff": m["shared_ff"]}}
+    lat = {"heads": m["heads"], "dim": m["lat_dim"], "rot_dim": m["lat_rot"], "vdim": m["lat_vdim"],
+           "kv_rank": m["kv_rank"], "scale": (m["lat_dim"] + m["lat_rot"]) ** -0.5,
+           "rot": {"base": 10000.0, "dims": m["lat_rot"]}}
+    kinds = [
+        lambda i: {"type": "mamba1", "mlp": dense,
+                   "mixer": {"inner": m["inner"], "state": m["state"], "dt_rank": m["dt_rank"], "conv": m["taps"]}},
+        lambda i: {"type": "attention", "mlp": moe,
+                   "mixer": {"heads": m["heads"], "kv_heads": m["kv_heads"], "dim": m["dim"], "vdim": m["dim"],
+                             "scale": m["dim"] ** -0.5, "rot": {"base": 10000.0, "dims": m["dim"] // 2},
+                             "mask": {"size": m["window"], "keep_first": m["keep_first"]}}},
+        lambda i: {"type": "latent_attention", "mlp": dense, "mixer": dict(lat)},
+        lambda i: {"type": "latent_attention", "mlp": moe, "mixer": dict(lat, kv_from=i - 1)},
+    ]
+    return {"architecture": "Bukatar", "vocab": q["vocab_size"], "width": q["hidden_size"], "norm": {"eps": 1e-6},
+            "max_positions": 4096, "layers": [kinds[i % 4](i) for i in range(layers)]}
+
+
+def kernel_points_bukatar(shape, batch, ctx_len, prefill_tokens, pk):
+    """The Bukatar design's own kernels beside the like kernels of Ritizen (the state-space walk and its
+    preparation, the attention's store, the sum that closes a sublayer) and of Qwen2 (attention, the gated
+    feed-forward's products) at the shape's sizes, each alone between CUDA events with L2 flushed:
+    milliseconds and the fraction of the roofline (measured copy bandwidth for kernels that stream, measured
+    bf16 product rate for the attention kernels and the products of a prompt)."""
+    import torch
+    from llm_inference_lab_b200.kernels import ops
+
+    dev = torch.device("cuda:0")
+    q, m, rz = SHAPES[shape], BUKATAR_SHAPES[shape], RITIZEN_SHAPES[shape]
+    width, ff = q["hidden_size"], q["intermediate_size"]
+    flush = torch.zeros((160 << 20,), dtype=torch.int16, device=dev)
+    bw, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    rows = {}
+
+    def record(name, ms, nbytes=None, flops=None):
+        entry = {"ms": round(ms, 4)}
+        if nbytes is not None:
+            entry.update(gbs=round(nbytes / (ms / 1e3) / 1e9, 1), frac_hbm=round(nbytes / (ms / 1e3) / bw, 4))
+        if flops is not None:
+            entry.update(tflops=round(flops / (ms / 1e3) / 1e12, 2), frac_bf16=round(flops / (ms / 1e3) / tf, 4))
+        rows[name] = entry
+
+    bf = lambda *s: (0.5 * torch.randn(*s, device=dev)).to(torch.bfloat16)  # noqa: E731
+    f32 = lambda *s: 0.5 * torch.randn(*s, device=dev)  # noqa: E731
+    for label, q_lens, pos0 in (("prefill", [prefill_tokens], [0]), ("decode", [1] * batch, [ctx_len] * batch)):
+        T, B = sum(q_lens), len(q_lens)
+        ctx, pages = bench_ctx(q_lens, pos0, PAGE_SIZE, dev)
+        # ---- the state-space mixer: convolution + SiLU, then the walk with a decay per channel and state entry
+        inner, N, taps = m["inner"], m["state"], m["taps"]
+        proj = f32(T, 2 * inner)
+        kept = torch.zeros(B, taps - 1, inner, device=dev)
+        cw, cb = bf(inner, taps), bf(inner)
+        ms = timed(lambda: ops.conv_silu(proj, 0, inner, taps, cw, cb, kept, ctx), flush=flush)
+        record(f"conv_silu {label}", ms, nbytes=T * inner * (4 + 4 + 2) + 2 * kept.numel() * 4)
+        x32, dt_pre, bc = f32(T, inner), f32(T, inner), f32(T, 2 * N)
+        a_log, skip, dtb = bf(inner, N), bf(inner), bf(inner)
+        state = torch.zeros(B, inner, N, device=dev)
+        ms = timed(lambda: ops.selective_scan(x32, dt_pre, bc, 0, N, proj[:, inner:], a_log, skip, dtb, state, ctx),
+                   flush=flush)
+        record(f"selective_scan {label}", ms, nbytes=T * (3 * inner * 4 + 2 * N * 4 + inner * 2) + 2 * state.numel() * 4,
+               flops=None if label == "decode" else 6.0 * T * inner * N)
+        # Ritizen's state-space walk (a decay per head and token) and its preparation, at its shape of the same name
+        H2, N2, V2, G2 = rz["ssm_heads"], rz["ssm_state"], rz["ssm_vdim"], rz["ssm_groups"]
+        conv = f32(T, H2 * V2 + 2 * G2 * N2)
+        a_tok, s_tok = torch.rand(T, H2, device=dev), torch.rand(T, H2, device=dev)
+        state2 = torch.zeros(B, H2, N2, V2, device=dev)
+        ms = timed(lambda: ops.decay_scan(conv[:, H2 * V2 + G2 * N2:], conv[:, H2 * V2: H2 * V2 + G2 * N2], conv[:, : H2 * V2],
+                                          state2, ctx, H2, G2, N2, V2, a_tok=a_tok, s_tok=s_tok), flush=flush)
+        record(f"ritizen decay_scan decay per token {label}", ms,
+               nbytes=T * (2 * G2 * N2 + 2 * H2 * V2 + 2 * H2) * 4 + 2 * state2.numel() * 4,
+               flops=None if label == "decode" else 4.0 * T * H2 * N2 * V2)
+        inner2, gn = H2 * V2, G2 * N2
+        sproj2 = f32(T, 2 * inner2 + 2 * gn + H2)
+        kept2 = torch.zeros(B, rz["taps"] - 1, inner2 + 2 * gn, device=dev)
+        tw, tb, hb = bf(inner2 + 2 * gn, rz["taps"]), bf(inner2 + 2 * gn), bf(H2)
+        ms = timed(lambda: ops.ssm_prepare(sproj2, inner2, 2 * inner2 + 2 * gn, inner2 + 2 * gn, rz["taps"], H2, tw, tb, hb,
+                                           hb, kept2, ctx), flush=flush)
+        record(f"ritizen ssm_prepare {label}", ms,
+               nbytes=T * ((inner2 + 2 * gn + H2) * 4 + (inner2 + 2 * gn + 2 * H2) * 4))
+        # ---- attention: bias + rotation of pairs + paged store, then the kernels with a window, kept first
+        # tokens and the denominator's extra one, beside plain causal attention over the same pages
+        nq, nkv, D = m["heads"], m["kv_heads"], m["dim"]
+        hd = ops.padded_head(D, D)
+        ck, cv = bf(pages, nkv, PAGE_SIZE, hd), bf(pages, nkv, PAGE_SIZE, hd)
+        aproj, ab = f32(T, (nq + nkv) * D), bf((nq + nkv) * D)
+        inv = torch.rand(D // 4, device=dev)
+        ms = timed(lambda: ops.rope_pairs_store(aproj, ab, ctx.row_pos, inv, D // 2, ctx.groups[0].row_slot, ck, cv, nq, nkv,
+                                                D, D, hd, nq * D, nq * D, torch.bfloat16), flush=flush)
+        record(f"rope_pairs_store {label}", ms, nbytes=T * ((nq + nkv) * D * 4 + (nq + 2 * nkv) * hd * 2))
+        wq, wk = bf(nq * D), bf(nkv * D)
+        aproj3, ab3 = f32(T, (nq + 2 * nkv) * D), bf((nq + 2 * nkv) * D)
+        ms = timed(lambda: ops.qk_norm_store(aproj3, ab3, wq, wk, ctx.groups[0].row_slot, ck, cv, nq, nkv, D, D, hd, 1e-6),
+                   flush=flush)
+        record(f"ritizen qk_norm_store {label}", ms, nbytes=T * ((nq + 2 * nkv) * D * 4 + (nq + 2 * nkv) * hd * 2))
+        qq = bf(T, nq * hd)
+        win, keep = m["window"], m["keep_first"]
+
+        def seen(pos):            # keys position `pos` sees through the window with kept first tokens
+            return min(pos + 1, win) + min(keep, max(0, pos + 1 - win))
+
+        all_pairs = sum(sum(p + i + 1 for i in range(n)) for p, n in zip(pos0, q_lens))
+        win_pairs = sum(sum(seen(p + i) for i in range(n)) for p, n in zip(pos0, q_lens))
+        win_keys = sum(min(p + n, win + n - 1 + keep) for p, n in zip(pos0, q_lens))
+        for name, kw, pairs, keys in (("causal", {}, all_pairs, sum(p + n for p, n in zip(pos0, q_lens))),
+                                      ("window + kept + one", dict(keep_first=keep, sink_one=True), win_pairs, win_keys)):
+            w_arg = win if kw else 0
+            ms = timed(lambda: ops.attention(qq, ck, cv, ctx, ctx.groups[0], nq, nkv, hd, w_arg, D ** -0.5, **kw), flush=flush)
+            record(f"attention {name} {label}", ms, nbytes=keys * 2 * nkv * hd * 2 + 2 * T * nq * hd * 2,
+                   flops=4.0 * pairs * nq * hd)
+        # ---- the feed-forwards: relu squared in the product's epilogue beside the gated product; the routed
+        # experts' kernels (pick, layout, grouped products, weighted sum) beside the dense products of equal rows
+        xb = bf(T, width)
+        w_up, w_gu, w_down = bf(ff, width), bf(2 * ff, width), bf(width, ff)
+        ms = timed(lambda: ops.linear(xb, w_up, None, act="relu2"), flush=flush)
+        record(f"product + relu squared {label}", ms, nbytes=(ff * width + T * (width + ff)) * 2, flops=2.0 * T * ff * width)
+        ms = timed(lambda: ops.linear_gated(xb, w_gu), flush=flush)
+        record(f"qwen2 gated product {label}", ms, nbytes=(2 * ff * width + T * (width + ff)) * 2,
+               flops=4.0 * T * ff * width)
+        hidden = bf(T, ff)
+        ms = timed(lambda: ops.linear(hidden, w_down, None, out_f32=True), flush=flush)
+        record(f"qwen2 down product {label}", ms, nbytes=(ff * width + T * ff) * 2 + T * width * 4, flops=2.0 * T * ff * width)
+        E, top, F = m["experts"], m["top"], m["expert_ff"]
+        logits = f32(T, E + 1)
+        ms = timed(lambda: ops.moe_route(logits, E, top, gate_col=E), flush=flush)
+        record(f"moe_route {label}", ms, nbytes=T * ((E + 1) * 4 + top * 8 + 4))
+        chosen, weight, gate = ops.moe_route(logits, E, top, gate_col=E)
+        ms = timed(lambda: ops.moe_layout(chosen, E, torch.bfloat16, width, F), flush=flush)
+        record(f"moe layout {label}", ms)
+        lay = ops.moe_layout(chosen, E, torch.bfloat16, width, F)
+        w_egu, w_ed = bf(E, 2 * F, width), bf(E, width, F)
+        used = min(E, T * top)
+        ms = timed(lambda: ops.moe_experts_up(xb, w_egu, lay, top), flush=flush)
+        record(f"grouped gated product {label}", ms, nbytes=(used * 2 * F * width + T * width + T * top * F) * 2,
+               flops=4.0 * T * top * F * width)
+        act = ops.moe_experts_up(xb, w_egu, lay, top)
+        ms = timed(lambda: ops.moe_experts_down(act, w_ed, lay), flush=flush)
+        record(f"grouped down product {label}", ms, nbytes=(used * F * width + T * top * F) * 2 + T * top * width * 4,
+               flops=2.0 * T * top * F * width)
+        y = ops.moe_experts_down(act, w_ed, lay)
+        shared = f32(T, width)
+        ms = timed(lambda: ops.moe_combine(y, lay.pos_of, weight, shared, gate), flush=flush)
+        record(f"moe_combine {label}", ms, nbytes=T * width * 4 * (top + 2))
+        # ---- the sum that closes a sublayer: x += norm(product), and the norm that opens the next one
+        x, a, w1 = f32(T, width), f32(T, width), bf(width)
+        ms = timed(lambda: ops.stream_norm_add(x, a, w1, 1e-6, next_weight=w1), flush=flush)
+        record(f"stream_norm_add + next norm {label}", ms, nbytes=T * width * (4 + 4 + 4 + 2))
+        ms = timed(lambda: ops.stream_norm_add(x, a, w1, 1e-6, copy=True), flush=flush)
+        record(f"ritizen stream_norm_add {label}", ms, nbytes=T * width * (4 + 4 + 4 + 2))
+        xq, delta = bf(T, width), bf(T, width)
+        ms = timed(lambda: ops.add_rmsnorm(xq, w1, 1e-6, delta=delta), flush=flush)
+        record(f"qwen2 add + norm {label}", ms, nbytes=T * width * 8)
+    ops.take_device_errors()
+    return rows
+
+
+def run_arch_bukatar(args):
+    shape, layers = args.shape, args.layers or 4
+    pk, pk_src = peaks()
+    qcfg = dict(SHAPES[shape], num_hidden_layers=layers)
+    folders = {"bukatar": arch_folder(bukatar_config(shape, layers), f"bukatar_{shape}_L{layers}"),
+               "ritizen": arch_folder(ritizen_config(shape, layers), f"ritizen_{shape}_L{layers}"),
+               "qwen2": model_folder(SHAPES[shape], layers)}
+    clocks = ClockSampler()
+    with clocks:
+        models = {name: model_points(folder, args.batch, args.prompt_len, PREFILL_TOKENS, 20)
+                  for name, folder in folders.items()}
+        kernels = kernel_points_bukatar(shape, args.batch, args.prompt_len + 512, PREFILL_TOKENS, pk)
+    print(json.dumps({
+        "arch": "bukatar", "beside": ["ritizen", "qwen2"], "shape": shape, "layers": layers, "batch": args.batch,
+        "prompt_len": args.prompt_len, "prefill_tokens": PREFILL_TOKENS, "dtype": "bf16",
+        "data": "synthetic: random weights N(0, 0.02) seed 0", "bukatar_mixers": BUKATAR_SHAPES[shape],
+        "hidden": qcfg["hidden_size"], "intermediate": qcfg["intermediate_size"], "vocab": qcfg["vocab_size"],
+        "models": models, "kernels": kernels, "peaks": dict(pk, source=pk_src), "clocks": clocks.summary()}))
+    return 0
+
+
 def kv_bytes_per_token(cfg, layers):
     d = cfg["hidden_size"] // cfg["num_attention_heads"]
     return 2 * layers * 2 * cfg["num_key_value_heads"] * d
@@ -798,11 +996,12 @@ def main() -> int:
     ap.add_argument("--stack-stamps", action="store_true",
                     help="run a few eager decode steps with the decode stack's in-kernel clock on and print what "
                          "each kind of phase took")
-    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "sogulix", "ritizen"],
+    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "sogulix", "ritizen", "bukatar"],
                     help="sogulix: instead of the headline run, prefill and decode throughput of the Sogulix design "
                          "beside Qwen2 at the layer sizes of --shape (0.5B or 1.5B; --layers, default 4), and each "
                          "of its kernels beside Qwen2's like kernel; prints its own line.  ritizen: the same for the "
-                         "Ritizen design, beside Sogulix and Qwen2")
+                         "Ritizen design, beside Sogulix and Qwen2; bukatar: the same for the Bukatar design, beside "
+                         "Ritizen and Qwen2")
     ap.add_argument("--only-prefill", type=int, default=0, metavar="TOKENS",
                     help="run only a prefill of TOKENS tokens a few times and print its time (for profiling)")
     args = ap.parse_args()
@@ -839,6 +1038,11 @@ def main() -> int:
             ap.error("--arch ritizen knows the shapes " + ", ".join(sorted(RITIZEN_SHAPES)))
         args.layers = 0 if args.layers == cfg["num_hidden_layers"] else args.layers
         return run_arch_ritizen(args)
+    if args.arch == "bukatar":
+        if args.shape not in BUKATAR_SHAPES:
+            ap.error("--arch bukatar knows the shapes " + ", ".join(sorted(BUKATAR_SHAPES)))
+        args.layers = 0 if args.layers == cfg["num_hidden_layers"] else args.layers
+        return run_arch_bukatar(args)
     folder = model_folder(cfg, args.layers)
     pk, pk_src = peaks()
     if args.serve:

@@ -110,6 +110,10 @@ struct Params {
   int m_tiles, n_tiles, splits;  // tiles on the M side, on the N side, and split-K planes
   QkvStore qkv;         // q/k/v epilogue only
   PickArgs pick;        // picking head only
+  // Grouped rows (tokens on the M side only): M-tile t meets the weight matrix tile_group[t], whose first row is
+  // tile_group[t] * group_rows of the weight operand; a tile whose group is -1 holds no rows and is skipped.
+  const int* tile_group;
+  int group_rows;
 };
 
 // Element offset of (slot, kv head) in a cache of [pages, n_kv, page_size, d], or -1 (no slot; a
@@ -253,21 +257,28 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     if (kt1 > p.k_tiles) kt1 = p.k_tiles;
     n_kt = kt1 > kt0 ? kt1 - kt0 : 0;
   };
+  // Grouped rows: the first weight row of the tile's group, or -1 for a tile to skip.  The table is written by
+  // an earlier kernel of the step: whoever reads it has waited for that kernel first.
+  auto weight_base = [&](int m0) -> int {
+    if (p.tile_group == nullptr) return 0;
+    const int g = p.tile_group[m0 / M_ROWS];
+    return g < 0 ? -1 : g * p.group_rows;
+  };
 
   if (warp == 0) {
     if (lane == 0) {
       // ---- producer: TMA loads ----
       // Weights do not depend on earlier kernels of the step: the first stages' weight tiles are
       // requested before the wait on the predecessor, the activation tiles after it.
-      auto load_weights = [&](int s, int kx, int m0, int n0) {
+      auto load_weights = [&](int s, int kx, int m0, int n0, int wb) {
         uint8_t* a_dst = tiles + s * S::STAGE_BYTES;
         uint8_t* b_dst = a_dst + S::A_BYTES;
         if (SWAP) {
           tma_load_2d(a_dst, &map_a, &full[s], kx, m0);
           if (GATED) tma_load_2d(a_dst + (TM / 2) * BK * 2, &map_a, &full[s], kx, p.up_offset + m0);
         } else {
-          tma_load_2d(b_dst, &map_b, &full[s], kx, n0);
-          if (GATED) tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_b, &full[s], kx, p.up_offset + n0);
+          tma_load_2d(b_dst, &map_b, &full[s], kx, wb + n0);
+          if (GATED) tma_load_2d(b_dst + (BN / 2) * BK * 2, &map_b, &full[s], kx, wb + p.up_offset + n0);
         }
       };
       auto load_activations = [&](int s, int kx, int m0, int n0) {
@@ -277,15 +288,18 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
       };
       int it = 0;  // stages filled so far, over all tiles
       bool first_tile = true, alive = true;
+      if (p.tile_group != nullptr) pdl_wait();
       for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
         int m0, n0, kt0, n_kt, split;
         locate(tile, m0, n0, kt0, n_kt, split);
+        const int wb = weight_base(m0);
+        if (wb < 0) continue;
         int i = 0;
         if (first_tile) {
           const int ahead = n_kt < S::STAGES ? n_kt : S::STAGES;
           for (; i < ahead; ++i) {  // the ring is empty: no wait
             mbar_expect_tx(&full[i], S::STAGE_BYTES);
-            load_weights(i, (kt0 + i) * BK, m0, n0);
+            load_weights(i, (kt0 + i) * BK, m0, n0, wb);
           }
           pdl_wait();
           for (int j = 0; j < ahead; ++j) load_activations(j, (kt0 + j) * BK, m0, n0);
@@ -298,7 +312,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) { alive = false; break; }
           mbar_expect_tx(&full[s], S::STAGE_BYTES);
           const int kx = (kt0 + i) * BK;
-          load_weights(s, kx, m0, n0);
+          load_weights(s, kx, m0, n0, wb);
           load_activations(s, kx, m0, n0);
         }
       }
@@ -320,11 +334,13 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
       auto wait_all = [&](uint64_t* bar, uint32_t parity) -> bool {
         return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
       };
-      int it = 0, local = 0;
+      int it = 0, local = 0;  // local: tiles this CTA has worked on (skipped ones do not count)
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+      if (p.tile_group != nullptr) pdl_wait();
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int m0, n0, kt0, n_kt, split;
         locate(tile, m0, n0, kt0, n_kt, split);
+        if (weight_base(m0) < 0) continue;
         const int buf = local % S::ACC_BUFS;
         const uint32_t use = (uint32_t)(local / S::ACC_BUFS);
         // the epilogue must have drained this accumulator (passes at once on its first use)
@@ -348,6 +364,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
           umma_commit(&empty[s]);  // the stage may be refilled once these MMAs have read it
         }
         umma_commit(&acc_full[buf]);  // the accumulator is complete once every MMA has retired
+        ++local;
       }
     }
   } else {
@@ -355,10 +372,12 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     const int quarter = warp & 3;
     constexpr int QROWS = TM / 4;            // tile rows in a quarter: one per lane
     pdl_wait();  // the output may still be read by an earlier kernel until it has completed
-    int local = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+    int local = -1;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       int m0, n0, kt0, n_kt, split;
       locate(tile, m0, n0, kt0, n_kt, split);
+      if (weight_base(m0) < 0) continue;
+      ++local;
       const int buf = local % S::ACC_BUFS;
       const uint32_t use = (uint32_t)(local / S::ACC_BUFS);
       const bool ok = mbar_wait(&acc_full[buf], use & 1, abort_flag);
@@ -795,6 +814,34 @@ LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* 
     if (out_f32) return dispatch_bn<PLAIN, true, float>(bn, ma, mb, p, grid, stream);
     return dispatch_bn<PLAIN, true, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
   }
+  if (out_f32) return dispatch_bn<PLAIN, false, float>(bn, ma, mb, p, grid, stream);
+  return dispatch_bn<PLAIN, false, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
+}
+
+// Rows grouped by the matrix they meet (routed experts), tokens on the M side: tile t of lab_gemm_tc_group_rows()
+// rows of x [rows, K] meets matrix tile_group[t] of w [groups, n_out (x2 when gated: gate rows, then up rows), K]
+// (-1: the tile holds no rows; it is skipped and its rows of `out` stay unwritten).  rows is a multiple of the
+// tile.  out: bf16 or f32 [rows, ld_out]; gated: silu(gate) * up, bf16 only.  bn: 64, 128 or 256.
+LAB_EXPORT int lab_gemm_tc_group_rows() { return BM; }
+LAB_EXPORT int lab_gemm_tc_grouped(void* out, const void* x, const void* w, int rows, int n_out, int K, int ldx,
+                                   int ld_out, int gated, int out_f32, int bn, int groups, const int* tile_group,
+                                   cudaStream_t stream) {
+  if (rows <= 0 || n_out <= 0) return 0;
+  if (rows % BM || groups <= 0 || tile_group == nullptr || (gated && out_f32)) return (int)cudaErrorInvalidValue;
+  if (K % 8 || ldx % 8 || K <= 0) return (int)cudaErrorInvalidValue;            // 16-byte rows for TMA
+  if ((((uintptr_t)x) | ((uintptr_t)w)) & 15) return (int)cudaErrorInvalidValue;  // 16-byte bases for TMA
+  const long long w_rows = (long long)groups * (gated ? 2 * n_out : n_out);
+  if (w_rows > 0x7fffffffll) return (int)cudaErrorInvalidValue;
+  CUtensorMap ma, mb;
+  Params p = {};
+  p.out = out;
+  p.ld_out = ld_out;
+  dim3 grid;
+  const int rc = set_up(p, ma, mb, grid, x, w, rows, n_out, (int)w_rows, K, ldx, gated, 0, bn, 1);
+  if (rc) return rc;
+  p.tile_group = tile_group;
+  p.group_rows = gated ? 2 * n_out : n_out;
+  if (gated) return dispatch_bn<GATED_SILU, false, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
   if (out_f32) return dispatch_bn<PLAIN, false, float>(bn, ma, mb, p, grid, stream);
   return dispatch_bn<PLAIN, false, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
 }

@@ -112,20 +112,23 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(int* __restrict__ row_s
 }
 
 // rows of the grouped layout as a matrix of their own (for products that cannot gather): out[r] = x[row_src[r] / top],
-// zeros where row_src is -1.  grid (rows).
+// zeros where row_src is -1.  grid (rows); 16 bytes a thread where the rows allow it (`vec`).
 template <typename T>
 __global__ void __launch_bounds__(128) moe_gather_kernel(T* __restrict__ out, const T* __restrict__ x,
-                                                         const int* __restrict__ row_src, int top, int width) {
+                                                         const int* __restrict__ row_src, int top, int width, int ldx,
+                                                         int vec) {
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x, src = row_src[r];
   T* dst = out + (size_t)r * width;
-  if (src < 0) {
-    for (int i = threadIdx.x; i < width; i += 128) dst[i] = from_f32<T>(0.f);
+  const T* row = src < 0 ? nullptr : x + (size_t)(src / top) * ldx;
+  if (vec) {
+    constexpr int PER = 16 / sizeof(T);
+    for (int i = threadIdx.x; i < width / PER; i += 128)
+      reinterpret_cast<uint4*>(dst)[i] = row ? reinterpret_cast<const uint4*>(row)[i] : make_uint4(0, 0, 0, 0);
     return;
   }
-  const T* row = x + (size_t)(src / top) * width;
-  for (int i = threadIdx.x; i < width; i += 128) dst[i] = row[i];
+  for (int i = threadIdx.x; i < width; i += 128) dst[i] = row ? row[i] : from_f32<T>(0.f);
 }
 
 // out[t] = sum_k weight[t, k] * y[pos_of[t, k]] (+ shared_gate[t] * shared[t]), all 32-bit.  grid (tokens).
@@ -171,14 +174,17 @@ LAB_EXPORT int lab_moe_align(int* row_src, int* tile_group, int* pos_of, const i
   LAB_LAUNCH_CHECK();
 }
 
-LAB_EXPORT int lab_moe_gather(void* out, const void* x, const int* row_src, int rows, int top, int width, int dtype,
-                              cudaStream_t stream) {
+LAB_EXPORT int lab_moe_gather(void* out, const void* x, const int* row_src, int rows, int top, int width, int ldx,
+                              int dtype, cudaStream_t stream) {
   if (rows <= 0) return 0;
+  const int per = dtype == LAB_F32 ? 4 : 8;
+  const int vec = width % per == 0 && ldx % per == 0 && ((((uintptr_t)out) | ((uintptr_t)x)) & 15) == 0;
   if (dtype == LAB_F32)
-    lab_launch(moe_gather_kernel<float>, dim3(rows), dim3(128), 0, stream, (float*)out, (const float*)x, row_src, top, width);
+    lab_launch(moe_gather_kernel<float>, dim3(rows), dim3(128), 0, stream, (float*)out, (const float*)x, row_src, top,
+               width, ldx, vec);
   else
     lab_launch(moe_gather_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, stream, (__nv_bfloat16*)out,
-               (const __nv_bfloat16*)x, row_src, top, width);
+               (const __nv_bfloat16*)x, row_src, top, width, ldx, vec);
   LAB_LAUNCH_CHECK();
 }
 

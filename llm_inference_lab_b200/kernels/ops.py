@@ -1482,6 +1482,75 @@ def moe_combine(y: torch.Tensor, pos_of: torch.Tensor, weight: torch.Tensor, sha
     return out
 
 
+GROUPED_KERNEL = "auto"     # "auto", "tc" (tcgen05, rows gathered first) or "plain" (ordinary units, gathering loads)
+GROUPED_TC_MIN_PAIRS = 256  # from this many (token, expert) pairs on, tiles of 128 rows are mostly full
+
+
+class MoeLayout:
+    """The (token, choice) pairs of a step in rows grouped by expert: `row_src` [rows] the pair at each row or -1,
+    `tile_group` [rows / tile] the expert of each tile of `tile` rows or -1, `pos_of` [pairs] each pair's row;
+    `tc`: the products run on the tensor cores (tiles of their 128 rows)."""
+    __slots__ = ("row_src", "tile_group", "pos_of", "rows", "tile", "tc", "experts")
+
+    def __init__(self, row_src, tile_group, pos_of, tile, tc, experts):
+        self.row_src, self.tile_group, self.pos_of = row_src, tile_group, pos_of
+        self.rows, self.tile, self.tc, self.experts = row_src.numel(), tile, tc, experts
+
+
+def moe_layout(chosen: torch.Tensor, experts: int, dtype: torch.dtype, width: int, expert_ff: int) -> MoeLayout:
+    """Lays a step's pairs out for the experts' products: on the tensor cores for bfloat16 steps with enough
+    pairs to fill tiles of 128 rows and sizes whose rows are whole 16-byte units, else on the ordinary units."""
+    pairs = chosen.numel()
+    tc = (GROUPED_KERNEL != "plain" and dtype == torch.bfloat16 and not _force_plain and width % 8 == 0
+          and expert_ff % 8 == 0 and (GROUPED_KERNEL == "tc" or pairs >= GROUPED_TC_MIN_PAIRS))
+    tile = int(lib("gemm_tc").lab_gemm_tc_group_rows()) if tc else grouped_tile_rows()
+    return MoeLayout(*moe_align(chosen, experts, tile), tile, tc, experts)
+
+
+def moe_gather(x: torch.Tensor, row_src: torch.Tensor, top: int) -> torch.Tensor:
+    """out[r] = x[row_src[r] // top]; zeros where row_src is -1."""
+    _on_gpu(x, row_src)
+    assert x.stride(1) == 1
+    out = torch.empty((row_src.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    _check(lib("moe").lab_moe_gather(_ptr(out), _ptr(x), _ptr(row_src), row_src.numel(), top, x.shape[1], x.stride(0),
+                                     dtype_code(x.dtype), _stream()), "moe_gather")
+    return out
+
+
+def linear_grouped_tc(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, gated: bool = False,
+                      out_f32: bool = False, bn: int | None = None) -> torch.Tensor:
+    """Row r of the result is x[r] times the matrix w[tile_group[r // 128]] transposed, on the tcgen05 tensor cores;
+    x [rows, K] bfloat16 with rows a multiple of 128, w as for `linear_grouped`.  Rows of tiles whose group is -1
+    are left unwritten."""
+    _on_gpu(x, w, tile_group)
+    rows, K = x.shape
+    N = w.shape[1] // 2 if gated else w.shape[1]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not _tc_operands(x, w[0]) or w.shape[2] != K:
+        raise KernelError("linear_grouped_tc takes bfloat16 operands with rows of whole 16-byte units")
+    assert w.is_contiguous() and w.dim() == 3 and tile_group.numel() * 128 == rows
+    out = torch.empty((rows, N), dtype=torch.float32 if out_f32 else torch.bfloat16, device=x.device)
+    if bn is None:
+        bn = 256 if gated else 128
+    _check(lib("gemm_tc").lab_gemm_tc_grouped(_ptr(out), _ptr(x), _ptr(w), rows, N, K, x.stride(0), out.stride(0),
+                                              int(gated), int(out_f32), bn, w.shape[0], _ptr(tile_group), _stream()),
+           "gemm_tc_grouped")
+    return out
+
+
+def moe_experts_up(x: torch.Tensor, w_gate_up: torch.Tensor, lay: MoeLayout, top: int) -> torch.Tensor:
+    """silu(W_gate h) * (W_up h) of every pair's token with its expert's matrices, [rows, expert_ff] in the layout."""
+    if lay.tc:
+        return linear_grouped_tc(moe_gather(x, lay.row_src, top), w_gate_up, lay.tile_group, gated=True)
+    return linear_grouped(x, w_gate_up, lay.row_src, top, lay.tile_group, lay.rows, gated=True)
+
+
+def moe_experts_down(act: torch.Tensor, w_down: torch.Tensor, lay: MoeLayout) -> torch.Tensor:
+    """W_down of every row's expert on `act` [rows, expert_ff], 32-bit [rows, width]."""
+    if lay.tc:
+        return linear_grouped_tc(act, w_down, lay.tile_group, out_f32=True)
+    return linear_grouped(act, w_down, None, 1, lay.tile_group, lay.rows, out_f32=True)
+
+
 def grouped_tile_rows() -> int:
     """Rows of a tile of the grouped product on the ordinary units."""
     return int(lib("gemm_plain").lab_gemm_plain_group_rows())

@@ -16,9 +16,10 @@ class RoutedExperts(FeedForward):
     with `shared_gate` multiplied by sigmoid(W_sg h), one number per token.
 
     The router's matrix and the gate's row are one product; one kernel picks, one lays the (token, expert)
-    pairs out in rows grouped by expert, two grouped products run the experts (the gather of the tokens' rows
-    is the first one's load), and one kernel forms the weighted sum, in the order of each token's choice, with
-    the shared expert's share.  The result is 32-bit."""
+    pairs out in rows grouped by expert, two grouped products run the experts, and one kernel forms the weighted
+    sum, in the order of each token's choice, with the shared expert's share.  Steps of many pairs in bfloat16
+    run the grouped products on the tensor cores over rows gathered into the layout; else the ordinary units
+    gather while they load.  The result is 32-bit."""
 
     NAMES = {"router": "router", "expert": "e{}.", "gate": "gate", "up": "up", "down": "down", "shared": "shared.",
              "shared_gate": "shared.sg"}
@@ -44,7 +45,7 @@ class RoutedExperts(FeedForward):
 
     @classmethod
     def libraries(cls, spec, dtype):
-        return [("moe", {})]
+        return [("moe", {})]       # the products' libraries belong to every model
 
     def __init__(self, spec, weights, dtype, device):
         super().__init__(spec, weights, dtype, device)
@@ -69,15 +70,13 @@ class RoutedExperts(FeedForward):
         E, top = self.experts, self.top
         logits = ops.linear(x, self.w_router, None, out_f32=True)
         chosen, weight, gate = ops.moe_route(logits, E, top, gate_col=E if self.gated_share else -1)
-        tile = ops.grouped_tile_rows()
-        row_src, tile_group, pos_of = ops.moe_align(chosen, E, tile)
-        rows = row_src.numel()
-        act = ops.linear_grouped(x, self.w_gate_up, row_src, top, tile_group, rows, gated=True)
-        y = ops.linear_grouped(act, self.w_down, None, 1, tile_group, rows, out_f32=True)
+        lay = ops.moe_layout(chosen, E, x.dtype, x.shape[1], self.ff)
+        act = ops.moe_experts_up(x, self.w_gate_up, lay, top)
+        y = ops.moe_experts_down(act, self.w_down, lay)
         shared = None
         if self.shared_ff:
             shared = ops.linear(ops.linear_gated(x, self.w_shared_gate_up), self.w_shared_down, None, out_f32=True)
-        return ops.moe_combine(y, pos_of, weight, shared, gate)
+        return ops.moe_combine(y, lay.pos_of, weight, shared, gate)
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)

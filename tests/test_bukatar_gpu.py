@@ -412,6 +412,46 @@ def test_router_layout_and_grouped_products(E, top, T):
     ops.take_device_errors()
 
 
+@pytest.mark.parametrize("E,top,T,K,F,force", [(6, 2, 40, 72, 40, True), (9, 3, 700, 136, 200, False),
+                                               (3, 1, 260, 64, 24, False), (16, 2, 9, 320, 264, True)])
+def test_grouped_products_on_the_tensor_cores(E, top, T, K, F, force):
+    """The experts' products on the tcgen05 kernel over rows gathered into tiles of 128: experts without a pair
+    (their tiles are skipped), experts with more than one tile, feature counts that are no multiple of a tile;
+    chosen by the layout itself from a few hundred pairs on, forced below that."""
+    torch = _torch()
+    from llm_inference_lab_b200.kernels import ops
+    rng = np.random.default_rng(E + T)
+    logits = rng.standard_normal((T, E)) * 2
+    logits[:, E // 2] = -50.0                                  # an expert nobody picks
+    if E > 4:
+        logits[: T // 2, 1] = 50.0                             # an expert half of the tokens pick
+    chosen, weight, _ = ops.moe_route(_t(logits), E, top)
+    ch = chosen.cpu().numpy()
+    dtype = torch.bfloat16
+    x = _t(rng.standard_normal((T, K)), dtype)
+    w_gu, w_down = _t(rng.standard_normal((E, 2 * F, K)) * 0.2, dtype), _t(rng.standard_normal((E, K, F)) * 0.2, dtype)
+    old = ops.GROUPED_KERNEL
+    ops.GROUPED_KERNEL = "tc" if force else "auto"
+    try:
+        lay = ops.moe_layout(chosen, E, dtype, K, F)
+        assert lay.tc and lay.tile == 128 and lay.rows % 128 == 0
+        act = ops.moe_experts_up(x, w_gu, lay, top)
+        y = ops.moe_experts_down(act, w_down, lay)
+    finally:
+        ops.GROUPED_KERNEL = old
+    out = _np(ops.moe_combine(y, lay.pos_of, weight, None, None))
+    act_np, rows = _np(act), lay.pos_of.cpu().numpy().reshape(T, top)
+    ref = np.zeros((T, K))
+    for t in range(T):
+        for k in range(top):
+            g = _np(w_gu[ch[t, k]])
+            hidden = pb.silu(_np(x[t]) @ g[:F].T) * (_np(x[t]) @ g[F:].T)
+            assert np.abs(act_np[rows[t, k]] - hidden).max() < 0.02 * max(1.0, np.abs(hidden).max()), (t, k)
+            ref[t] += _np(weight)[t, k] * (_np(_t(hidden, dtype)) @ _np(w_down[ch[t, k]]).T)
+    assert np.abs(out - ref).max() < 0.02 * max(1.0, np.abs(ref).max())
+    ops.take_device_errors()
+
+
 # ---------------------------------------------------------------------------------------------
 # whole models under every cut
 # ---------------------------------------------------------------------------------------------
