@@ -144,6 +144,146 @@ int launch_heads_few(void* out, const void* x, const void* w, int M, int N, int 
                          head_x, head_o);
 }
 
+// Grouped rows for few rows (a decode step's pairs of token and expert): the tiles above would walk K in steps
+// of 16 behind a barrier each for a handful of live rows.  Here a CTA takes one tile of the layout and 8 (gated)
+// or 16 output columns; a warp reads its two weight rows once, 16 bytes a lane where the rows allow it, for up
+// to GF_ROWS live rows of the tile, whose inputs wait in shared memory in 32-bit; each row's sums close with a
+// shuffle tree.  More live rows take further passes.  Rows whose source is -1 stay unwritten.
+constexpr int GF_ROWS = 8;      // live rows a pass takes
+constexpr int GF_KC = 1024;     // inputs of a row that wait in shared memory at a time
+constexpr int GF_TILE_MAX = 128;
+
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float* v) {
+    const float4 q = *reinterpret_cast<const float4*>(p);
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(u[i] << 16);
+      v[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+    }
+  }
+};
+
+template <typename T, typename OutT, bool GATED>
+__global__ void __launch_bounds__(256) gemm_grouped_few_kernel(OutT* __restrict__ out, const T* __restrict__ x,
+                                                               const T* __restrict__ w, int M, int N, int K, int ldx,
+                                                               int ldo, long long group_w,
+                                                               const int* __restrict__ row_src, int row_div,
+                                                               int gather, const int* __restrict__ tile_group,
+                                                               int tile, int vec) {
+  __shared__ float xs[GF_ROWS][GF_KC];
+  __shared__ int live_row[GF_TILE_MAX], live_x[GF_TILE_MAX];
+  __shared__ int n_live_s;
+  pdl_trigger();
+  pdl_wait();
+  const int group = tile_group[blockIdx.y];
+  if (group < 0) return;
+  w += (long long)group * group_w;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, m0 = blockIdx.y * tile;
+  if (tid == 0) {
+    int cnt = 0;
+    for (int i = 0; i < tile && m0 + i < M; ++i) {
+      const int src = row_src[m0 + i];
+      if (src < 0) continue;
+      live_row[cnt] = m0 + i;
+      live_x[cnt++] = gather ? src / row_div : m0 + i;
+    }
+    n_live_s = cnt;
+  }
+  __syncthreads();
+  const int n_live = n_live_s;
+  // the warp's two weight rows: gate and up of one column, or two neighbouring columns
+  const int n_a = GATED ? blockIdx.x * 8 + warp : (blockIdx.x * 8 + warp) * 2;
+  const int n_b = GATED ? n_a : n_a + 1;
+  const bool has_a = n_a < N, has_b = n_b < N;
+  const T* row_a = w + (size_t)(has_a ? n_a : 0) * K;
+  const T* row_b = w + (size_t)(GATED ? N + (has_a ? n_a : 0) : (has_b ? n_b : 0)) * K;
+  for (int r0 = 0; r0 < n_live; r0 += GF_ROWS) {
+    const int rows = min(GF_ROWS, n_live - r0);
+    float acc_a[GF_ROWS], acc_b[GF_ROWS];
+#pragma unroll
+    for (int t = 0; t < GF_ROWS; ++t) acc_a[t] = acc_b[t] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += GF_KC) {
+      const int kc = min(GF_KC, K - k0);
+      __syncthreads();      // whoever still read the inputs before is done
+      for (int t = 0; t < rows; ++t) {
+        const T* src = x + (size_t)live_x[r0 + t] * ldx + k0;
+        for (int k = tid; k < kc; k += 256) xs[t][k] = to_f32<T>(src[k]);
+      }
+      __syncthreads();
+      if (!has_a) continue;
+      if (vec) {
+        constexpr int V = Vec16<T>::N;
+        for (int k = lane * V; k < kc; k += 32 * V) {
+          float wa[V], wb[V];
+          Vec16<T>::load(row_a + k0 + k, wa);
+          Vec16<T>::load(row_b + k0 + k, wb);
+#pragma unroll
+          for (int t = 0; t < GF_ROWS; ++t) {
+            if (t < rows) {
+#pragma unroll
+              for (int e = 0; e < V; ++e) {
+                const float xv = xs[t][k + e];
+                acc_a[t] = fmaf(wa[e], xv, acc_a[t]);
+                acc_b[t] = fmaf(wb[e], xv, acc_b[t]);
+              }
+            }
+          }
+        }
+      } else {
+        for (int k = lane; k < kc; k += 32) {
+          const float wa = to_f32<T>(row_a[k0 + k]), wb = to_f32<T>(row_b[k0 + k]);
+#pragma unroll
+          for (int t = 0; t < GF_ROWS; ++t)
+            if (t < rows) {
+              acc_a[t] = fmaf(wa, xs[t][k], acc_a[t]);
+              acc_b[t] = fmaf(wb, xs[t][k], acc_b[t]);
+            }
+        }
+      }
+    }
+    if (!has_a) continue;
+#pragma unroll
+    for (int t = 0; t < GF_ROWS; ++t) {
+      if (t >= rows) break;
+      const float a = warp_sum(acc_a[t]), b = warp_sum(acc_b[t]);
+      if (lane != 0) continue;
+      OutT* dst = out + (size_t)live_row[r0 + t] * ldo;
+      if (GATED) {
+        dst[n_a] = from_f32<OutT>(a / (1.f + expf(-a)) * b);
+      } else {
+        dst[n_a] = from_f32<OutT>(a);
+        if (has_b) dst[n_b] = from_f32<OutT>(b);
+      }
+    }
+  }
+}
+
+template <typename T, typename OutT>
+int launch_grouped_few(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo, int gated,
+                       long long group_w, const int* row_src, int row_div, int gather, const int* tile_group, int tile,
+                       cudaStream_t stream) {
+  constexpr int V = 16 / (int)sizeof(T);
+  const int vec = K % V == 0 && ((uintptr_t)w & 15) == 0;
+  const int cols = gated ? 8 : 16;
+  dim3 grid((N + cols - 1) / cols, (M + tile - 1) / tile);
+  if (gated)
+    return (int)lab_launch(gemm_grouped_few_kernel<T, OutT, true>, grid, dim3(256), 0, stream, (OutT*)out, (const T*)x,
+                           (const T*)w, M, N, K, ldx, ldo, group_w, row_src, row_div, gather, tile_group, tile, vec);
+  return (int)lab_launch(gemm_grouped_few_kernel<T, OutT, false>, grid, dim3(256), 0, stream, (OutT*)out, (const T*)x,
+                         (const T*)w, M, N, K, ldx, ldo, group_w, row_src, row_div, gather, tile_group, tile, vec);
+}
+
 template <typename T, typename OutT>
 int launch(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx, int ldo, int gated,
            cudaStream_t stream, int batch = 1, long long batch_x = 0, long long batch_w = 0, long long batch_o = 0,
@@ -210,4 +350,25 @@ LAB_EXPORT int lab_gemm_plain_grouped(void* out, const void* x, const void* w, i
                                         row_div, tile_group);
   return launch<__nv_bfloat16, __nv_bfloat16>(out, x, w, nullptr, M, N, K, ldx, ldo, gated, stream, 1, 0, group_w, 0,
                                               row_src, row_div, tile_group);
+}
+
+// The same product for few rows (a decode step): tile t of `tile` rows (at most 128) meets matrix tile_group[t];
+// only rows whose row_src is not -1 are formed and written.  gather: row m reads x's row row_src[m] / row_div,
+// else x's row m.
+LAB_EXPORT int lab_gemm_plain_grouped_few(void* out, const void* x, const void* w, int M, int N, int K, int ldx,
+                                          int ldo, int gated, long long group_w, const int* row_src, int row_div,
+                                          int gather, const int* tile_group, int tile, int dtype, int out_f32,
+                                          cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (tile_group == nullptr || row_src == nullptr || row_div < 1 || tile < 1 || tile > GF_TILE_MAX || K <= 0)
+    return (int)cudaErrorInvalidValue;
+  if ((M + tile - 1) / tile > 65535) return (int)cudaErrorInvalidValue;
+  if (dtype == LAB_F32)
+    return launch_grouped_few<float, float>(out, x, w, M, N, K, ldx, ldo, gated, group_w, row_src, row_div, gather,
+                                            tile_group, tile, stream);
+  if (out_f32)
+    return launch_grouped_few<__nv_bfloat16, float>(out, x, w, M, N, K, ldx, ldo, gated, group_w, row_src, row_div,
+                                                    gather, tile_group, tile, stream);
+  return launch_grouped_few<__nv_bfloat16, __nv_bfloat16>(out, x, w, M, N, K, ldx, ldo, gated, group_w, row_src,
+                                                          row_div, gather, tile_group, tile, stream);
 }

@@ -9,8 +9,11 @@
 //
 // Kernels: the causal convolution of x with the request's last inputs kept between steps (+ SiLU), and
 // the walk.  The walk is sequential in tokens; a CTA takes 16 channels of one request, 8 lanes a channel,
-// each lane a share of the state's entries in registers; a chunk of tokens waits in shared memory (step
-// sizes formed once per channel while it is brought in); the sum over the state closes with three shuffles.
+// each lane a share of the state's entries in registers.  A chunk of tokens waits in shared memory while the
+// next one arrives there (cp.async); step sizes are formed once per channel and token before the chunk is
+// walked.  From token to token passes only the state's own update: every lane leaves its share of the sum
+// over the state in shared memory, and the sums, the skip term and the gate are formed after the chunk, a
+// thread per channel and token.
 #include "common.cuh"
 
 namespace {
@@ -102,18 +105,25 @@ struct ScanParams {
   int ld_x, ld_dt, ld_bc, ld_z, b_at, c_at, channels, N, n_slots, write, ld_out;
 };
 
+// 4 bytes from global to shared memory without a register in between; waited for by cp_async_wait_all.
+__device__ __forceinline__ void cp_async_f32(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+
+// Floats of one chunk's inputs as they arrive: dt_pre, x, z [WT][WC] each, then B and C [WT][N] each.
+__host__ __device__ inline int scan_chunk_floats(int N) { return 3 * WT * WC + 2 * WT * N; }
+
 template <typename T, int R>
 __global__ void __launch_bounds__(WTHREADS) selective_scan_kernel(T* __restrict__ out, const T* __restrict__ a_log,
                                                                   const T* __restrict__ skip,
                                                                   const T* __restrict__ dt_bias, ScanParams p) {
   extern __shared__ float smem[];
-  float* s_dt = smem;                    // [WT][WC] step sizes
-  float* s_dx = s_dt + WT * WC;          // [WT][WC] step size times x
-  float* s_x = s_dx + WT * WC;           // [WT][WC]
-  float* s_z = s_x + WT * WC;            // [WT][WC]
-  float* s_y = s_z + WT * WC;            // [WT][WC] results of the chunk
-  float* s_b = s_y + WT * WC;            // [WT][N]
-  float* s_c = s_b + WT * p.N;           // [WT][N]
+  const int N = p.N, chunk_floats = scan_chunk_floats(N);
+  float* s_in = smem;                          // two chunks of inputs: one walked, one arriving
+  float* s_dx = smem + 2 * chunk_floats;       // [WT][WC] step size times x
+  float* s_part = s_dx + WT * WC;              // [WT][WC][WL] every lane's share of the sum over the state
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.y, c0 = blockIdx.x * WC;
@@ -130,7 +140,25 @@ __global__ void __launch_bounds__(WTHREADS) selective_scan_kernel(T* __restrict_
     if (tid == 0) lab_set_error(LAB_ERR_PAGE_RANGE);
     return;
   }
-  const int N = p.N;
+  // a chunk's inputs set out for shared memory; channels beyond the last read nothing and stay unused
+  auto fetch = [&](int t0, float* buf) {
+    const int nt = min(WT, n - t0);
+    float *b_dt = buf, *b_x = buf + WT * WC, *b_z = buf + 2 * WT * WC, *b_b = buf + 3 * WT * WC, *b_c = b_b + WT * N;
+    for (int i = tid; i < nt * WC; i += WTHREADS) {
+      const int cc = c0 + i % WC;
+      if (cc >= p.channels) continue;
+      const size_t row = (size_t)(first + t0 + i / WC);
+      cp_async_f32(b_dt + i, p.dt_pre + row * p.ld_dt + cc);
+      cp_async_f32(b_x + i, p.x + row * p.ld_x + cc);
+      cp_async_f32(b_z + i, p.z + row * p.ld_z + cc);
+    }
+    for (int i = tid; i < nt * N; i += WTHREADS) {
+      const float* row = p.bc + (size_t)(first + t0 + i / N) * p.ld_bc + i % N;
+      cp_async_f32(b_b + i, row + p.b_at);
+      cp_async_f32(b_c + i, row + p.c_at);
+    }
+  };
+  fetch(0, s_in);
   float S[R], A[R];
   float* st = p.state + ((size_t)slot * p.channels + (live ? c : 0)) * N;
 #pragma unroll
@@ -140,50 +168,52 @@ __global__ void __launch_bounds__(WTHREADS) selective_scan_kernel(T* __restrict_
     S[i] = has ? st[e] : 0.f;
     A[i] = has ? -expf(to_f32(a_log[(size_t)c * N + e])) : 0.f;
   }
-  const float d_skip = live ? to_f32(skip[c]) : 0.f;
-  for (int t0 = 0; t0 < n; t0 += WT) {
+  int which = 0;
+  for (int t0 = 0; t0 < n; t0 += WT, which ^= 1) {
     const int nt = min(WT, n - t0);
-    __syncthreads();       // the chunk before has been read and its results written out
+    float* buf = s_in + which * chunk_floats;
+    float *b_dt = buf, *b_x = buf + WT * WC, *b_z = buf + 2 * WT * WC, *b_b = buf + 3 * WT * WC, *b_c = b_b + WT * N;
+    cp_async_wait_all();
+    __syncthreads();       // the chunk is here; the chunk before has been written out, its buffer is free
+    if (t0 + WT < n) fetch(t0 + WT, s_in + (which ^ 1) * chunk_floats);
+    // step sizes once per channel and token
     for (int i = tid; i < nt * WC; i += WTHREADS) {
-      const int tt = i / WC, cc = c0 + i % WC;
-      const size_t row = (size_t)(first + t0 + tt);
-      float dt = 0.f, xv = 0.f, zv = 0.f;
+      const int cc = c0 + i % WC;
+      float dt = 0.f, dx = 0.f;
       if (cc < p.channels) {
-        dt = softplus_f(p.dt_pre[row * p.ld_dt + cc] + to_f32(dt_bias[cc]));
-        xv = p.x[row * p.ld_x + cc];
-        zv = p.z[row * p.ld_z + cc];
+        dt = softplus_f(b_dt[i] + to_f32(dt_bias[cc]));
+        dx = dt * b_x[i];
       }
-      s_dt[i] = dt;
-      s_dx[i] = dt * xv;
-      s_x[i] = xv;
-      s_z[i] = zv;
-    }
-    for (int i = tid; i < nt * N; i += WTHREADS) {
-      const size_t row = (size_t)(first + t0 + i / N) * p.ld_bc;
-      s_b[i] = p.bc[row + p.b_at + i % N];
-      s_c[i] = p.bc[row + p.c_at + i % N];
+      b_dt[i] = dt;
+      s_dx[i] = dx;
     }
     __syncthreads();
+    // the walk: nothing but the state's own update passes from token to token
+#pragma unroll 4
     for (int tt = 0; tt < nt; ++tt) {
-      const float dt = s_dt[tt * WC + ch], dx = s_dx[tt * WC + ch];
+      const float dt = b_dt[tt * WC + ch], dx = s_dx[tt * WC + ch];
       float acc = 0.f;
 #pragma unroll
       for (int i = 0; i < R; ++i) {
         const int e = i * WL + l;
         if (e < N) {
-          S[i] = fmaf(expf(dt * A[i]), S[i], dx * s_b[tt * N + e]);
-          acc = fmaf(S[i], s_c[tt * N + e], acc);
+          S[i] = fmaf(expf(dt * A[i]), S[i], dx * b_b[tt * N + e]);
+          acc = fmaf(S[i], b_c[tt * N + e], acc);
         }
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      if (l == 0) s_y[tt * WC + ch] = fmaf(d_skip, s_x[tt * WC + ch], acc) * silu_f(s_z[tt * WC + ch]);
+      s_part[tt * WTHREADS + tid] = acc;
     }
     __syncthreads();
-    for (int i = tid; i < nt * WC; i += WTHREADS)
-      if (c0 + i % WC < p.channels)
-        out[(size_t)(first + t0 + i / WC) * p.ld_out + c0 + i % WC] = from_f32<T>(s_y[i]);
+    // the sum over the lanes (in their order), the skip term and the gate, a thread per channel and token
+    for (int i = tid; i < nt * WC; i += WTHREADS) {
+      const int cc = c0 + i % WC;
+      if (cc >= p.channels) continue;
+      const float4 lo = *reinterpret_cast<const float4*>(s_part + (size_t)i * WL);
+      const float4 hi = *reinterpret_cast<const float4*>(s_part + (size_t)i * WL + 4);
+      const float acc = ((lo.x + hi.x) + (lo.z + hi.z)) + ((lo.y + hi.y) + (lo.w + hi.w));
+      out[(size_t)(first + t0 + i / WC) * p.ld_out + cc] =
+          from_f32<T>(fmaf(to_f32(skip[cc]), b_x[i], acc) * silu_f(b_z[i]));
+    }
   }
   if (p.write && live) {
 #pragma unroll
@@ -197,7 +227,7 @@ __global__ void __launch_bounds__(WTHREADS) selective_scan_kernel(T* __restrict_
 template <typename T, int R>
 int launch_scan(void* out, const void* a_log, const void* skip, const void* dt_bias, const ScanParams& p, int requests,
                 cudaStream_t stream) {
-  const size_t smem = sizeof(float) * ((size_t)5 * WT * WC + (size_t)2 * WT * p.N);
+  const size_t smem = sizeof(float) * ((size_t)2 * scan_chunk_floats(p.N) + (size_t)WT * WC + (size_t)WT * WC * WL);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(selective_scan_kernel<T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;

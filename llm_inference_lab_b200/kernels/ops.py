@@ -1482,29 +1482,33 @@ def moe_combine(y: torch.Tensor, pos_of: torch.Tensor, weight: torch.Tensor, sha
     return out
 
 
-GROUPED_KERNEL = "auto"     # "auto", "tc" (tcgen05, rows gathered first) or "plain" (ordinary units, gathering loads)
+GROUPED_KERNEL = "auto"     # "auto", "tc" (tcgen05, rows gathered first), "plain" (ordinary units) or "tiles" (their tiled kernel only)
 GROUPED_TC_MIN_PAIRS = 256  # from this many (token, expert) pairs on, tiles of 128 rows are mostly full
+GROUPED_FEW_MAX_PAIRS = 64  # up to this many pairs (a decode step) the ordinary units read each weight row once
 
 
 class MoeLayout:
     """The (token, choice) pairs of a step in rows grouped by expert: `row_src` [rows] the pair at each row or -1,
     `tile_group` [rows / tile] the expert of each tile of `tile` rows or -1, `pos_of` [pairs] each pair's row;
-    `tc`: the products run on the tensor cores (tiles of their 128 rows)."""
-    __slots__ = ("row_src", "tile_group", "pos_of", "rows", "tile", "tc", "experts")
+    `tc`: the products run on the tensor cores (tiles of their 128 rows); `few`: on the ordinary units by the
+    kernel for a handful of rows."""
+    __slots__ = ("row_src", "tile_group", "pos_of", "rows", "tile", "tc", "few", "experts")
 
-    def __init__(self, row_src, tile_group, pos_of, tile, tc, experts):
+    def __init__(self, row_src, tile_group, pos_of, tile, tc, few, experts):
         self.row_src, self.tile_group, self.pos_of = row_src, tile_group, pos_of
-        self.rows, self.tile, self.tc, self.experts = row_src.numel(), tile, tc, experts
+        self.rows, self.tile, self.tc, self.few, self.experts = row_src.numel(), tile, tc, few, experts
 
 
 def moe_layout(chosen: torch.Tensor, experts: int, dtype: torch.dtype, width: int, expert_ff: int) -> MoeLayout:
     """Lays a step's pairs out for the experts' products: on the tensor cores for bfloat16 steps with enough
-    pairs to fill tiles of 128 rows and sizes whose rows are whole 16-byte units, else on the ordinary units."""
+    pairs to fill tiles of 128 rows and sizes whose rows are whole 16-byte units, else on the ordinary units (a
+    step of few pairs by the kernel that reads each weight row once for a tile's live rows)."""
     pairs = chosen.numel()
     tc = (GROUPED_KERNEL != "plain" and dtype == torch.bfloat16 and not _force_plain and width % 8 == 0
           and expert_ff % 8 == 0 and (GROUPED_KERNEL == "tc" or pairs >= GROUPED_TC_MIN_PAIRS))
+    few = not tc and GROUPED_KERNEL != "tiles" and pairs <= GROUPED_FEW_MAX_PAIRS
     tile = int(lib("gemm_tc").lab_gemm_tc_group_rows()) if tc else grouped_tile_rows()
-    return MoeLayout(*moe_align(chosen, experts, tile), tile, tc, experts)
+    return MoeLayout(*moe_align(chosen, experts, tile), tile, tc, few, experts)
 
 
 def moe_gather(x: torch.Tensor, row_src: torch.Tensor, top: int) -> torch.Tensor:
@@ -1541,6 +1545,8 @@ def moe_experts_up(x: torch.Tensor, w_gate_up: torch.Tensor, lay: MoeLayout, top
     """silu(W_gate h) * (W_up h) of every pair's token with its expert's matrices, [rows, expert_ff] in the layout."""
     if lay.tc:
         return linear_grouped_tc(moe_gather(x, lay.row_src, top), w_gate_up, lay.tile_group, gated=True)
+    if lay.few:
+        return linear_grouped_few(x, w_gate_up, lay.row_src, top, True, lay.tile_group, lay.tile, gated=True)
     return linear_grouped(x, w_gate_up, lay.row_src, top, lay.tile_group, lay.rows, gated=True)
 
 
@@ -1548,7 +1554,27 @@ def moe_experts_down(act: torch.Tensor, w_down: torch.Tensor, lay: MoeLayout) ->
     """W_down of every row's expert on `act` [rows, expert_ff], 32-bit [rows, width]."""
     if lay.tc:
         return linear_grouped_tc(act, w_down, lay.tile_group, out_f32=True)
+    if lay.few:
+        return linear_grouped_few(act, w_down, lay.row_src, 1, False, lay.tile_group, lay.tile, out_f32=True)
     return linear_grouped(act, w_down, None, 1, lay.tile_group, lay.rows, out_f32=True)
+
+
+def linear_grouped_few(x: torch.Tensor, w: torch.Tensor, row_src: torch.Tensor, row_div: int, gather: bool,
+                       tile_group: torch.Tensor, tile: int, gated: bool = False, out_f32: bool = False) -> torch.Tensor:
+    """`linear_grouped` for a handful of rows: only rows whose `row_src` is not -1 are formed (the others stay
+    unwritten); `gather`: row r reads x[row_src[r] // row_div], else x[r]."""
+    _on_gpu(x, w, row_src, tile_group)
+    rows, K = row_src.numel(), x.shape[1]
+    N = w.shape[1] // 2 if gated else w.shape[1]
+    assert w.is_contiguous() and w.dim() == 3 and w.shape[2] == K and w.dtype == x.dtype and x.stride(1) == 1
+    assert gather or x.shape[0] >= rows
+    odt = torch.float32 if (out_f32 or x.dtype == torch.float32) else x.dtype
+    out = torch.empty((rows, N), dtype=odt, device=x.device)
+    _check(lib("gemm_plain").lab_gemm_plain_grouped_few(
+        _ptr(out), _ptr(x), _ptr(w), rows, N, K, x.stride(0), out.stride(0), int(gated),
+        ctypes.c_longlong(w.shape[1] * K), _ptr(row_src), int(row_div), int(gather), _ptr(tile_group), int(tile),
+        dtype_code(x.dtype), int(out_f32), _stream()), "gemm_plain_grouped_few")
+    return out
 
 
 def grouped_tile_rows() -> int:

@@ -412,6 +412,42 @@ def test_router_layout_and_grouped_products(E, top, T):
     ops.take_device_errors()
 
 
+@pytest.mark.parametrize("E,top,T,K,F", [(5, 2, 3, 24, 10), (4, 1, 1, 1100, 7), (3, 3, 20, 2088, 33), (7, 2, 30, 41, 19)])
+def test_grouped_products_for_few_rows(E, top, T, K, F):
+    """The experts' products by the kernel for a handful of rows: rows of whole 16-byte units and others, more
+    inputs than wait in shared memory at a time, an odd count of columns, experts with more live rows than a
+    pass takes and experts with none; against the plain products, and the layout picks it for such a step."""
+    torch = _torch()
+    from llm_inference_lab_b200.kernels import ops
+    rng = np.random.default_rng(E + K)
+    logits = rng.standard_normal((T, E)) * 2
+    if T > 8:
+        logits[: T - 2, 0] = 40.0                              # one expert takes most tokens: several passes
+        logits[:, E - 1] = -40.0                               # and one takes none
+    chosen, weight, _ = ops.moe_route(_t(logits), E, top)
+    ch = chosen.cpu().numpy()
+    for dtype in _dtypes():
+        lay = ops.moe_layout(chosen, E, dtype, K, F)
+        assert lay.few and not lay.tc
+        x = _t(rng.standard_normal((T, K)), dtype)
+        w_gu = _t(rng.standard_normal((E, 2 * F, K)) * K ** -0.5, dtype)
+        w_down = _t(rng.standard_normal((E, K, F)) * 0.3, dtype)
+        act = ops.moe_experts_up(x, w_gu, lay, top)
+        y = ops.moe_experts_down(act, w_down, lay)
+        out = _np(ops.moe_combine(y, lay.pos_of, weight, None, None))
+        rows = lay.pos_of.cpu().numpy().reshape(T, top)
+        ref = np.zeros((T, K))
+        tol = 1e-4 if dtype == torch.float32 else 0.03
+        for t in range(T):
+            for k in range(top):
+                g = _np(w_gu[ch[t, k]])
+                hidden = pb.silu(_np(x[t]) @ g[:F].T) * (_np(x[t]) @ g[F:].T)
+                assert np.abs(_np(act[rows[t, k]]) - hidden).max() < tol * max(1.0, np.abs(hidden).max()), (t, k)
+                ref[t] += _np(weight)[t, k] * (_np(act[rows[t, k]]) @ _np(w_down[ch[t, k]]).T)
+        assert np.abs(out - ref).max() < (1e-4 if dtype == torch.float32 else 0.01) * max(1.0, np.abs(ref).max())
+    ops.take_device_errors()
+
+
 @pytest.mark.parametrize("E,top,T,K,F,force", [(6, 2, 40, 72, 40, True), (9, 3, 700, 136, 200, False),
                                                (3, 1, 260, 64, 24, False), (16, 2, 9, 320, 264, True)])
 def test_grouped_products_on_the_tensor_cores(E, top, T, K, F, force):
