@@ -145,8 +145,8 @@ int launch_heads_few(void* out, const void* x, const void* w, int M, int N, int 
 }
 
 // Grouped rows for few rows (a decode step's pairs of token and expert): the tiles above would walk K in steps
-// of 16 behind a barrier each for a handful of live rows.  Here a CTA takes one tile of the layout and 8 (gated)
-// or 16 output columns; a warp reads its two weight rows once, 16 bytes a lane where the rows allow it, for up
+// of 16 behind a barrier each for a handful of live rows.  Here a CTA takes one tile of the layout and 16 (gated)
+// or 32 output columns; a warp reads its four weight rows once, 16 bytes a lane where the rows allow it, for up
 // to GF_ROWS live rows of the tile, whose inputs wait in shared memory in 32-bit; each row's sums close with a
 // shuffle tree.  More live rows take further passes.  Rows whose source is -1 stay unwritten.
 constexpr int GF_ROWS = 8;      // live rows a pass takes
@@ -190,29 +190,46 @@ __global__ void __launch_bounds__(256) gemm_grouped_few_kernel(OutT* __restrict_
   if (group < 0) return;
   w += (long long)group * group_w;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, m0 = blockIdx.y * tile;
-  if (tid == 0) {
-    int cnt = 0;
-    for (int i = 0; i < tile && m0 + i < M; ++i) {
-      const int src = row_src[m0 + i];
-      if (src < 0) continue;
-      live_row[cnt] = m0 + i;
-      live_x[cnt++] = gather ? src / row_div : m0 + i;
+  // the tile's live rows in their order: a thread a row, places from the warps' ballots
+  __shared__ int warp_live[GF_TILE_MAX / 32];
+  const int my_src = (tid < tile && m0 + tid < M) ? row_src[m0 + tid] : -1;
+  const unsigned ballot = __ballot_sync(0xffffffffu, my_src >= 0);
+  if (tid < GF_TILE_MAX && lane == 0) warp_live[warp] = __popc(ballot);
+  __syncthreads();
+  if (tid < GF_TILE_MAX) {
+    int at = __popc(ballot & ((1u << lane) - 1u)), all = 0;
+#pragma unroll
+    for (int i = 0; i < GF_TILE_MAX / 32; ++i) {
+      if (i < warp) at += warp_live[i];
+      all += warp_live[i];
     }
-    n_live_s = cnt;
+    if (my_src >= 0) {
+      live_row[at] = m0 + tid;
+      live_x[at] = gather ? my_src / row_div : m0 + tid;
+    }
+    if (tid == 0) n_live_s = all;
   }
   __syncthreads();
   const int n_live = n_live_s;
-  // the warp's two weight rows: gate and up of one column, or two neighbouring columns
-  const int n_a = GATED ? blockIdx.x * 8 + warp : (blockIdx.x * 8 + warp) * 2;
-  const int n_b = GATED ? n_a : n_a + 1;
-  const bool has_a = n_a < N, has_b = n_b < N;
-  const T* row_a = w + (size_t)(has_a ? n_a : 0) * K;
-  const T* row_b = w + (size_t)(GATED ? N + (has_a ? n_a : 0) : (has_b ? n_b : 0)) * K;
+  // the warp's four weight rows: gate and up of two neighbouring columns, or four neighbouring columns
+  constexpr int NR = 4;
+  const int n0 = (blockIdx.x * 8 + warp) * (GATED ? 2 : NR);
+  int col[NR];
+  const T* wrow[NR];
+#pragma unroll
+  for (int r = 0; r < NR; ++r) {
+    col[r] = GATED ? n0 + (r >> 1) : n0 + r;
+    const int c = col[r] < N ? col[r] : 0;        // a row beyond the last reads row 0; its sums are dropped
+    wrow[r] = w + (size_t)(GATED && (r & 1) ? N + c : c) * K;
+  }
+  const bool any = n0 < N;
   for (int r0 = 0; r0 < n_live; r0 += GF_ROWS) {
     const int rows = min(GF_ROWS, n_live - r0);
-    float acc_a[GF_ROWS], acc_b[GF_ROWS];
+    float acc[NR][GF_ROWS];
 #pragma unroll
-    for (int t = 0; t < GF_ROWS; ++t) acc_a[t] = acc_b[t] = 0.f;
+    for (int r = 0; r < NR; ++r)
+#pragma unroll
+      for (int t = 0; t < GF_ROWS; ++t) acc[r][t] = 0.f;
     for (int k0 = 0; k0 < K; k0 += GF_KC) {
       const int kc = min(GF_KC, K - k0);
       __syncthreads();      // whoever still read the inputs before is done
@@ -221,49 +238,57 @@ __global__ void __launch_bounds__(256) gemm_grouped_few_kernel(OutT* __restrict_
         for (int k = tid; k < kc; k += 256) xs[t][k] = to_f32<T>(src[k]);
       }
       __syncthreads();
-      if (!has_a) continue;
+      if (!any) continue;
       if (vec) {
         constexpr int V = Vec16<T>::N;
         for (int k = lane * V; k < kc; k += 32 * V) {
-          float wa[V], wb[V];
-          Vec16<T>::load(row_a + k0 + k, wa);
-          Vec16<T>::load(row_b + k0 + k, wb);
+          float wv[NR][V];
+#pragma unroll
+          for (int r = 0; r < NR; ++r) Vec16<T>::load(wrow[r] + k0 + k, wv[r]);
 #pragma unroll
           for (int t = 0; t < GF_ROWS; ++t) {
             if (t < rows) {
 #pragma unroll
               for (int e = 0; e < V; ++e) {
                 const float xv = xs[t][k + e];
-                acc_a[t] = fmaf(wa[e], xv, acc_a[t]);
-                acc_b[t] = fmaf(wb[e], xv, acc_b[t]);
+#pragma unroll
+                for (int r = 0; r < NR; ++r) acc[r][t] = fmaf(wv[r][e], xv, acc[r][t]);
               }
             }
           }
         }
       } else {
         for (int k = lane; k < kc; k += 32) {
-          const float wa = to_f32<T>(row_a[k0 + k]), wb = to_f32<T>(row_b[k0 + k]);
+          float wv[NR];
+#pragma unroll
+          for (int r = 0; r < NR; ++r) wv[r] = to_f32<T>(wrow[r][k0 + k]);
 #pragma unroll
           for (int t = 0; t < GF_ROWS; ++t)
             if (t < rows) {
-              acc_a[t] = fmaf(wa, xs[t][k], acc_a[t]);
-              acc_b[t] = fmaf(wb, xs[t][k], acc_b[t]);
+              const float xv = xs[t][k];
+#pragma unroll
+              for (int r = 0; r < NR; ++r) acc[r][t] = fmaf(wv[r], xv, acc[r][t]);
             }
         }
       }
     }
-    if (!has_a) continue;
+    if (!any) continue;
 #pragma unroll
     for (int t = 0; t < GF_ROWS; ++t) {
       if (t >= rows) break;
-      const float a = warp_sum(acc_a[t]), b = warp_sum(acc_b[t]);
+      float v[NR];
+#pragma unroll
+      for (int r = 0; r < NR; ++r) v[r] = warp_sum(acc[r][t]);
       if (lane != 0) continue;
       OutT* dst = out + (size_t)live_row[r0 + t] * ldo;
       if (GATED) {
-        dst[n_a] = from_f32<OutT>(a / (1.f + expf(-a)) * b);
+#pragma unroll
+        for (int c = 0; c < NR / 2; ++c)
+          if (col[2 * c] < N) dst[col[2 * c]] = from_f32<OutT>(v[2 * c] / (1.f + expf(-v[2 * c])) * v[2 * c + 1]);
       } else {
-        dst[n_a] = from_f32<OutT>(a);
-        if (has_b) dst[n_b] = from_f32<OutT>(b);
+#pragma unroll
+        for (int r = 0; r < NR; ++r)
+          if (col[r] < N) dst[col[r]] = from_f32<OutT>(v[r]);
       }
     }
   }
@@ -275,7 +300,7 @@ int launch_grouped_few(void* out, const void* x, const void* w, int M, int N, in
                        cudaStream_t stream) {
   constexpr int V = 16 / (int)sizeof(T);
   const int vec = K % V == 0 && ((uintptr_t)w & 15) == 0;
-  const int cols = gated ? 8 : 16;
+  const int cols = gated ? 16 : 32;      // 8 warps, four weight rows each
   dim3 grid((N + cols - 1) / cols, (M + tile - 1) / tile);
   if (gated)
     return (int)lab_launch(gemm_grouped_few_kernel<T, OutT, true>, grid, dim3(256), 0, stream, (OutT*)out, (const T*)x,

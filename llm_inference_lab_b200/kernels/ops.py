@@ -1483,8 +1483,11 @@ def moe_combine(y: torch.Tensor, pos_of: torch.Tensor, weight: torch.Tensor, sha
 
 
 GROUPED_KERNEL = "auto"     # "auto", "tc" (tcgen05, rows gathered first), "plain" (ordinary units) or "tiles" (their tiled kernel only)
-GROUPED_TC_MIN_PAIRS = 256  # from this many (token, expert) pairs on, tiles of 128 rows are mostly full
-GROUPED_FEW_MAX_PAIRS = 64  # up to this many pairs (a decode step) the ordinary units read each weight row once
+# The experts' products of a step, measured with 8 experts of the 0.5B sizes: the few-rows kernel grows with the
+# pairs (62 us at 16, 111 us at 64, 298 us at 254), the tensor cores stay near 60 to 70 us from 16 pairs to 512
+# (a tile of 128 rows costs the same part empty), the tiled kernel on the ordinary units near 370 us.
+GROUPED_FEW_MAX_PAIRS = 24        # up to this many pairs the few-rows kernel is ahead of the tensor cores
+GROUPED_FEW_MAX_PAIRS_PLAIN = 256  # and up to this many ahead of the tiled kernel, where the tensor cores cannot serve
 
 
 class MoeLayout:
@@ -1500,13 +1503,15 @@ class MoeLayout:
 
 
 def moe_layout(chosen: torch.Tensor, experts: int, dtype: torch.dtype, width: int, expert_ff: int) -> MoeLayout:
-    """Lays a step's pairs out for the experts' products: on the tensor cores for bfloat16 steps with enough
-    pairs to fill tiles of 128 rows and sizes whose rows are whole 16-byte units, else on the ordinary units (a
-    step of few pairs by the kernel that reads each weight row once for a tile's live rows)."""
+    """Lays a step's pairs out for the experts' products: a handful of pairs (a small decode step) for the few-rows
+    kernel on the ordinary units; more on the tensor cores, for bfloat16 and sizes whose rows are whole 16-byte
+    units; else on the ordinary units, few-rows up to a few hundred pairs and tiled beyond."""
     pairs = chosen.numel()
-    tc = (GROUPED_KERNEL != "plain" and dtype == torch.bfloat16 and not _force_plain and width % 8 == 0
-          and expert_ff % 8 == 0 and (GROUPED_KERNEL == "tc" or pairs >= GROUPED_TC_MIN_PAIRS))
-    few = not tc and GROUPED_KERNEL != "tiles" and pairs <= GROUPED_FEW_MAX_PAIRS
+    can_tc = (GROUPED_KERNEL not in ("plain", "tiles") and dtype == torch.bfloat16 and not _force_plain and width % 8 == 0
+              and expert_ff % 8 == 0)
+    tc = can_tc and (GROUPED_KERNEL == "tc" or pairs > GROUPED_FEW_MAX_PAIRS)
+    few = (not tc and GROUPED_KERNEL != "tiles"
+           and pairs <= (GROUPED_FEW_MAX_PAIRS if can_tc else GROUPED_FEW_MAX_PAIRS_PLAIN))
     tile = int(lib("gemm_tc").lab_gemm_tc_group_rows()) if tc else grouped_tile_rows()
     return MoeLayout(*moe_align(chosen, experts, tile), tile, tc, few, experts)
 
