@@ -15,7 +15,9 @@
 // query - key < window; a negative `window` means chunks of that many positions, see
 // `lab_first_key`) is this engine's addition, and so are two options of a window: `keep_first` (the first
 // that many positions stay visible to every later query, at their true positions) and `sink` (1: one is
-// added to the softmax's denominator, a key with score 0 and no value).
+// added to the softmax's denominator, a key with score 0 and no value; with `sinks`, a number per query head,
+// exp(sinks[h]) instead), and `dist_bias` [n_q, bias_len]: a number per head and distance query - key that is
+// added to the scaled score, distances from bias_len - 1 on sharing the last entry.
 #include "common.cuh"
 
 namespace {
@@ -27,7 +29,8 @@ __global__ void __launch_bounds__(WARPS * 32) attention_plain_kernel(
     T* __restrict__ out, int out_stride, const T* __restrict__ q, int q_stride, const T* __restrict__ cache_k,
     const T* __restrict__ cache_v, const int* __restrict__ row_req, const int* __restrict__ row_pos,
     const int* __restrict__ block_table, int max_blocks, int n_q, int n_kv, int d, int page_size, int num_pages,
-    int window, float scale, int keep_first, int sink) {
+    int window, float scale, int keep_first, int sink, const float* __restrict__ sinks,
+    const float* __restrict__ dist_bias, int bias_len) {
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
@@ -66,6 +69,7 @@ __global__ void __launch_bounds__(WARPS * 32) attention_plain_kernel(
         float dot = 0.f;
         for (int i = 0; i < d; ++i) dot = fmaf(qs[i], to_f32<T>(kr[i]), dot);
         s = dot * scale;
+        if (dist_bias != nullptr) s += dist_bias[(size_t)h * bias_len + min(p - j, bias_len - 1)];
       }
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -103,9 +107,10 @@ __global__ void __launch_bounds__(WARPS * 32) attention_plain_kernel(
   __syncthreads();
   float big = -INFINITY;
   for (int w = 0; w < WARPS; ++w) big = fmaxf(big, part[w * (d + 2) + d]);
-  if (sink) big = fmaxf(big, 0.f);
+  const float sink_at = sinks != nullptr ? sinks[h] : 0.f;      // the score of the key without a value
+  if (sink) big = fmaxf(big, sink_at);
   for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    float num = 0.f, den = sink ? expf(-big) : 0.f;
+    float num = 0.f, den = sink ? expf(sink_at - big) : 0.f;
     for (int w = 0; w < WARPS; ++w) {
       const float mw = part[w * (d + 2) + d];
       const float wt = (mw == -INFINITY) ? 0.f : expf(mw - big);
@@ -120,19 +125,21 @@ __global__ void __launch_bounds__(WARPS * 32) attention_plain_kernel(
 LAB_EXPORT int lab_attention_plain(void* out, int out_stride, const void* q, int q_stride, const void* cache_k,
                                    const void* cache_v, const int* row_req, const int* row_pos, const int* block_table,
                                    int max_blocks, int tokens, int n_q, int n_kv, int d, int page_size, int num_pages,
-                                   int window, float scale, int keep_first, int sink, int dtype,
-                                   cudaStream_t stream) {
+                                   int window, float scale, int keep_first, int sink, const float* sinks,
+                                   const float* dist_bias, int bias_len, int dtype, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (d > 32 * MAX_DPL || d <= 0 || n_q % n_kv) return (int)cudaErrorInvalidValue;
+  if (d > 32 * MAX_DPL || d <= 0 || n_q % n_kv || (dist_bias != nullptr && bias_len < 1)) return (int)cudaErrorInvalidValue;
+  if (sinks != nullptr) sink = 1;
   dim3 grid(tokens, n_q);
   const size_t smem = (size_t)(d + WARPS * (d + 2)) * sizeof(float);
   if (dtype == LAB_F32)
     return (int)lab_launch(attention_plain_kernel<float>, grid, dim3(WARPS * 32), smem, stream, (float*)out, out_stride,
                            (const float*)q, q_stride, (const float*)cache_k, (const float*)cache_v, row_req, row_pos,
                            block_table, max_blocks, n_q, n_kv, d, page_size, num_pages, window, scale, keep_first,
-                           sink);
+                           sink, sinks, dist_bias, bias_len);
   return (int)lab_launch(attention_plain_kernel<__nv_bfloat16>, grid, dim3(WARPS * 32), smem, stream,
                          (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
                          (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v, row_req, row_pos, block_table,
-                         max_blocks, n_q, n_kv, d, page_size, num_pages, window, scale, keep_first, sink);
+                         max_blocks, n_q, n_kv, d, page_size, num_pages, window, scale, keep_first, sink, sinks, dist_bias,
+                         bias_len);
 }

@@ -98,6 +98,17 @@ __device__ __forceinline__ float lab_act(float z, int code) {
   return r * r;
 }
 
+// The gate of a gated pair of products, by its limit: 0, silu(g) * u; a positive limit, the capped form with
+// g' = min(g, limit) and u' = clamp(u, -limit, limit): g' * sigmoid(1.702 g') * (u' + 1).
+__device__ __forceinline__ float gate_pair(float g, float u, float limit) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+  }
+  return g / (1.f + expf(-g)) * u;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);

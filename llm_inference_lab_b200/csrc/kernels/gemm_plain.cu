@@ -20,7 +20,7 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(OutT* __restrict__ out,
                                                          int N, int K, int ldx, int ldo, long long batch_x,
                                                          long long batch_w, long long batch_o, int gelu,
                                                          const int* __restrict__ row_src, int row_div,
-                                                         const int* __restrict__ tile_group) {
+                                                         const int* __restrict__ tile_group, float gate_limit) {
   pdl_trigger();
   pdl_wait();
   // a batch of products of one shape (blockIdx.z): operand b lies b * batch_* elements further on
@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(256) gemm_plain_kernel(OutT* __restrict__ out,
       float v;
       if (GATED) {
         const float g = acc[0][i][j], u = acc[GATED ? 1 : 0][i][j];
-        v = g / (1.f + expf(-g)) * u;
+        v = gate_pair(g, u, gate_limit);
       } else {
         v = acc[0][i][j] + (bias ? to_f32<T>(bias[n]) : 0.f);
         if (gelu) v = lab_act(v, gelu);      // the activation after the bias, before the rounding
@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(256) gemm_grouped_few_kernel(OutT* __restrict_
                                                                int ldo, long long group_w,
                                                                const int* __restrict__ row_src, int row_div,
                                                                int gather, const int* __restrict__ tile_group,
-                                                               int tile, int vec) {
+                                                               int tile, int vec, float gate_limit) {
   __shared__ float xs[GF_ROWS][GF_KC];
   __shared__ int live_row[GF_TILE_MAX], live_x[GF_TILE_MAX];
   __shared__ int n_live_s;
@@ -284,7 +284,7 @@ __global__ void __launch_bounds__(256) gemm_grouped_few_kernel(OutT* __restrict_
       if (GATED) {
 #pragma unroll
         for (int c = 0; c < NR / 2; ++c)
-          if (col[2 * c] < N) dst[col[2 * c]] = from_f32<OutT>(v[2 * c] / (1.f + expf(-v[2 * c])) * v[2 * c + 1]);
+          if (col[2 * c] < N) dst[col[2 * c]] = from_f32<OutT>(gate_pair(v[2 * c], v[2 * c + 1], gate_limit));
       } else {
 #pragma unroll
         for (int r = 0; r < NR; ++r)
@@ -297,41 +297,46 @@ __global__ void __launch_bounds__(256) gemm_grouped_few_kernel(OutT* __restrict_
 template <typename T, typename OutT>
 int launch_grouped_few(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo, int gated,
                        long long group_w, const int* row_src, int row_div, int gather, const int* tile_group, int tile,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, float gate_limit) {
   constexpr int V = 16 / (int)sizeof(T);
   const int vec = K % V == 0 && ((uintptr_t)w & 15) == 0;
   const int cols = gated ? 16 : 32;      // 8 warps, four weight rows each
   dim3 grid((N + cols - 1) / cols, (M + tile - 1) / tile);
   if (gated)
     return (int)lab_launch(gemm_grouped_few_kernel<T, OutT, true>, grid, dim3(256), 0, stream, (OutT*)out, (const T*)x,
-                           (const T*)w, M, N, K, ldx, ldo, group_w, row_src, row_div, gather, tile_group, tile, vec);
+                           (const T*)w, M, N, K, ldx, ldo, group_w, row_src, row_div, gather, tile_group, tile, vec,
+                           gate_limit);
   return (int)lab_launch(gemm_grouped_few_kernel<T, OutT, false>, grid, dim3(256), 0, stream, (OutT*)out, (const T*)x,
-                         (const T*)w, M, N, K, ldx, ldo, group_w, row_src, row_div, gather, tile_group, tile, vec);
+                         (const T*)w, M, N, K, ldx, ldo, group_w, row_src, row_div, gather, tile_group, tile, vec, 0.f);
 }
 
 template <typename T, typename OutT>
 int launch(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx, int ldo, int gated,
            cudaStream_t stream, int batch = 1, long long batch_x = 0, long long batch_w = 0, long long batch_o = 0,
-           const int* row_src = nullptr, int row_div = 1, const int* tile_group = nullptr) {
+           const int* row_src = nullptr, int row_div = 1, const int* tile_group = nullptr, float gate_limit = 0.f) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
   if (gated == 1)
     return (int)lab_launch(gemm_plain_kernel<T, OutT, true>, grid, dim3(256), 0, stream, (OutT*)out, (const T*)x,
                            (const T*)w, (const T*)nullptr, M, N, K, ldx, ldo, batch_x, batch_w, batch_o, 0, row_src,
-                           row_div, tile_group);
+                           row_div, tile_group, gate_limit);
   return (int)lab_launch(gemm_plain_kernel<T, OutT, false>, grid, dim3(256), 0, stream, (OutT*)out, (const T*)x,
                          (const T*)w, (const T*)bias, M, N, K, ldx, ldo, batch_x, batch_w, batch_o,
-                         gated >= 2 ? gated - 1 : 0, row_src, row_div, tile_group);
+                         gated >= 2 ? gated - 1 : 0, row_src, row_div, tile_group, 0.f);
 }
 }  // namespace
 
 // N is the number of output columns; with gated == 1, w holds 2 N rows (gate rows, then up rows); gated == 2 is
 // the plain product with GELU (tanh form) after the bias, 3 with the square of relu.
 LAB_EXPORT int lab_gemm_plain(void* out, const void* x, const void* w, const void* bias, int M, int N, int K, int ldx,
-                              int ldo, int gated, int dtype, int out_f32, cudaStream_t stream) {
+                              int ldo, int gated, int dtype, int out_f32, float gate_limit, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (dtype == LAB_F32) return launch<float, float>(out, x, w, bias, M, N, K, ldx, ldo, gated, stream);
-  if (out_f32) return launch<__nv_bfloat16, float>(out, x, w, bias, M, N, K, ldx, ldo, gated, stream);
-  return launch<__nv_bfloat16, __nv_bfloat16>(out, x, w, bias, M, N, K, ldx, ldo, gated, stream);
+  if (dtype == LAB_F32)
+    return launch<float, float>(out, x, w, bias, M, N, K, ldx, ldo, gated, stream, 1, 0, 0, 0, nullptr, 1, nullptr, gate_limit);
+  if (out_f32)
+    return launch<__nv_bfloat16, float>(out, x, w, bias, M, N, K, ldx, ldo, gated, stream, 1, 0, 0, 0, nullptr, 1, nullptr,
+                                        gate_limit);
+  return launch<__nv_bfloat16, __nv_bfloat16>(out, x, w, bias, M, N, K, ldx, ldo, gated, stream, 1, 0, 0, 0, nullptr, 1,
+                                              nullptr, gate_limit);
 }
 
 // `batch` products of one shape in one launch: out_b[m, n] = sum_k x_b[m, k] * w_b[n, k], operand b lying
@@ -364,17 +369,18 @@ LAB_EXPORT int lab_gemm_plain_batched(void* out, const void* x, const void* w, i
 LAB_EXPORT int lab_gemm_plain_group_rows() { return BM; }
 LAB_EXPORT int lab_gemm_plain_grouped(void* out, const void* x, const void* w, int M, int N, int K, int ldx, int ldo,
                                       int gated, long long group_w, const int* row_src, int row_div,
-                                      const int* tile_group, int dtype, int out_f32, cudaStream_t stream) {
+                                      const int* tile_group, int dtype, int out_f32, float gate_limit,
+                                      cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (tile_group == nullptr || row_div < 1) return (int)cudaErrorInvalidValue;
   if (dtype == LAB_F32)
     return launch<float, float>(out, x, w, nullptr, M, N, K, ldx, ldo, gated, stream, 1, 0, group_w, 0, row_src, row_div,
-                                tile_group);
+                                tile_group, gate_limit);
   if (out_f32)
     return launch<__nv_bfloat16, float>(out, x, w, nullptr, M, N, K, ldx, ldo, gated, stream, 1, 0, group_w, 0, row_src,
-                                        row_div, tile_group);
+                                        row_div, tile_group, gate_limit);
   return launch<__nv_bfloat16, __nv_bfloat16>(out, x, w, nullptr, M, N, K, ldx, ldo, gated, stream, 1, 0, group_w, 0,
-                                              row_src, row_div, tile_group);
+                                              row_src, row_div, tile_group, gate_limit);
 }
 
 // The same product for few rows (a decode step): tile t of `tile` rows (at most 128) meets matrix tile_group[t];
@@ -383,17 +389,17 @@ LAB_EXPORT int lab_gemm_plain_grouped(void* out, const void* x, const void* w, i
 LAB_EXPORT int lab_gemm_plain_grouped_few(void* out, const void* x, const void* w, int M, int N, int K, int ldx,
                                           int ldo, int gated, long long group_w, const int* row_src, int row_div,
                                           int gather, const int* tile_group, int tile, int dtype, int out_f32,
-                                          cudaStream_t stream) {
+                                          float gate_limit, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (tile_group == nullptr || row_src == nullptr || row_div < 1 || tile < 1 || tile > GF_TILE_MAX || K <= 0)
     return (int)cudaErrorInvalidValue;
   if ((M + tile - 1) / tile > 65535) return (int)cudaErrorInvalidValue;
   if (dtype == LAB_F32)
     return launch_grouped_few<float, float>(out, x, w, M, N, K, ldx, ldo, gated, group_w, row_src, row_div, gather,
-                                            tile_group, tile, stream);
+                                            tile_group, tile, stream, gate_limit);
   if (out_f32)
     return launch_grouped_few<__nv_bfloat16, float>(out, x, w, M, N, K, ldx, ldo, gated, group_w, row_src, row_div,
-                                                    gather, tile_group, tile, stream);
+                                                    gather, tile_group, tile, stream, gate_limit);
   return launch_grouped_few<__nv_bfloat16, __nv_bfloat16>(out, x, w, M, N, K, ldx, ldo, gated, group_w, row_src,
-                                                          row_div, gather, tile_group, tile, stream);
+                                                          row_div, gather, tile_group, tile, stream, gate_limit);
 }

@@ -107,6 +107,7 @@ struct Params {
   int k_tiles;          // k-tiles in total
   int k_tiles_per_split;
   int up_offset;        // gated: row offset of the "up" half inside the weight matrix
+  float gate_limit;     // gated: 0, silu(gate) * up; positive, the capped form (`silu_gate` with a limit)
   int m_tiles, n_tiles, splits;  // tiles on the M side, on the N side, and split-K planes
   QkvStore qkv;         // q/k/v epilogue only
   PickArgs pick;        // picking head only
@@ -498,7 +499,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
               tmem_ld32_issue(lane_addr + BN / 2 + c * 32, ru);
               tmem_wait();
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = silu_gate(__uint_as_float(r[j]), __uint_as_float(ru[j]));
+              for (int j = 0; j < 32; ++j) v[j] = silu_gate(__uint_as_float(r[j]), __uint_as_float(ru[j]), p.gate_limit);
             } else {
               tmem_wait();
 #pragma unroll
@@ -596,7 +597,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             const int tok = n0 + col;
             if (tok >= p.n_rows) break;
             dst[(size_t)tok * p.ld_out] =
-                __float2bfloat16_rn(silu_gate(exchange[f * (BN + 1) + col], exchange[(HALF + f) * (BN + 1) + col]));
+                __float2bfloat16_rn(silu_gate(exchange[f * (BN + 1) + col], exchange[(HALF + f) * (BN + 1) + col], p.gate_limit));
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");  // the buffer is free for the next tile
@@ -782,9 +783,10 @@ __global__ void wait_probe_kernel(unsigned long long limit_ns, int* gave_up) {
 // [splits, tokens, ld_out] of floats (no bias, not gated).
 // swap != 0: features on the M side (few tokens); bn: tile of the N side (16..256).
 // gated: 0 the plain product, 1 the SiLU-gated pair, 2 the plain product with GELU (tanh form) after the bias, 3 with the square of relu.
+// gate_limit (gated 1): 0, silu(gate) * up; positive, gate and up capped at the limit, sigmoid(1.702 gate), up + 1.
 LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* bias, int tokens, int n_out, int K,
                            int ldx, int ld_out, int gated, int out_f32, int swap, int bn, int splits,
-                           cudaStream_t stream) {
+                           float gate_limit, cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
   const int gelu = gated >= 2 ? gated - 1 : 0;      // 1: GELU, 2: the square of relu
   if (gelu) gated = 0;
@@ -797,6 +799,7 @@ LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* 
   p.out = out;
   p.bias = (const __nv_bfloat16*)bias;
   p.gelu = gelu;
+  p.gate_limit = gate_limit;
   p.ld_out = ld_out;
   p.split_stride = splits > 1 ? (long long)tokens * ld_out : 0;
   dim3 grid;
@@ -825,7 +828,7 @@ LAB_EXPORT int lab_gemm_tc(void* out, const void* x, const void* w, const void* 
 LAB_EXPORT int lab_gemm_tc_group_rows() { return BM; }
 LAB_EXPORT int lab_gemm_tc_grouped(void* out, const void* x, const void* w, int rows, int n_out, int K, int ldx,
                                    int ld_out, int gated, int out_f32, int bn, int groups, const int* tile_group,
-                                   cudaStream_t stream) {
+                                   float gate_limit, cudaStream_t stream) {
   if (rows <= 0 || n_out <= 0) return 0;
   if (rows % BM || groups <= 0 || tile_group == nullptr || (gated && out_f32)) return (int)cudaErrorInvalidValue;
   if (K % 8 || ldx % 8 || K <= 0) return (int)cudaErrorInvalidValue;            // 16-byte rows for TMA
@@ -840,6 +843,7 @@ LAB_EXPORT int lab_gemm_tc_grouped(void* out, const void* x, const void* w, int 
   const int rc = set_up(p, ma, mb, grid, x, w, rows, n_out, (int)w_rows, K, ldx, gated, 0, bn, 1);
   if (rc) return rc;
   p.tile_group = tile_group;
+  p.gate_limit = gate_limit;
   p.group_rows = gated ? 2 * n_out : n_out;
   if (gated) return dispatch_bn<GATED_SILU, false, __nv_bfloat16>(bn, ma, mb, p, grid, stream);
   if (out_f32) return dispatch_bn<PLAIN, false, float>(bn, ma, mb, p, grid, stream);

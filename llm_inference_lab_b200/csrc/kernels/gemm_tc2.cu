@@ -99,6 +99,7 @@ struct Params {
   int k_tiles;          // k-tiles in total
   int k_tiles_per_split;
   int up_offset;        // gated: row offset of the "up" half inside the weight matrix
+  float gate_limit;     // gated: 0, silu(gate) * up; positive, the capped form (`silu_gate` with a limit)
   int m_tiles, n_tiles, splits;  // tiles of 256 tokens, tiles of output features, split-K planes
 };
 
@@ -261,7 +262,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
             tmem_ld32_issue(lane_addr + BN / 2 + c * 32, ru);
             tmem_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = silu_gate(__uint_as_float(r[j]), __uint_as_float(ru[j]));
+            for (int j = 0; j < 32; ++j) v[j] = silu_gate(__uint_as_float(r[j]), __uint_as_float(ru[j]), p.gate_limit);
           } else {
             tmem_wait();
 #pragma unroll
@@ -428,7 +429,8 @@ int pick_bn(int tokens, int n_out, bool gated, int splits) {
 // bn: accumulator columns of a tile, 256, 224 or 192; 0: the width that fills the rounds of the pairs best.
 // gated: 0 the plain product, 1 the SiLU-gated pair, 2 the plain product with GELU (tanh form) after the bias, 3 with the square of relu.
 LAB_EXPORT int lab_gemm_tc2(void* out, const void* x, const void* w, const void* bias, int tokens, int n_out, int K,
-                            int ldx, int ld_out, int gated, int out_f32, int splits, int bn, cudaStream_t stream) {
+                            int ldx, int ld_out, int gated, int out_f32, int splits, int bn, float gate_limit,
+                            cudaStream_t stream) {
   if (tokens <= 0 || n_out <= 0) return 0;
   const int gelu = gated >= 2 ? gated - 1 : 0;      // 1: GELU, 2: the square of relu
   if (gelu) gated = 0;
@@ -448,6 +450,7 @@ LAB_EXPORT int lab_gemm_tc2(void* out, const void* x, const void* w, const void*
   p.out = out;
   p.bias = (const __nv_bfloat16*)bias;
   p.gelu = gelu;
+  p.gate_limit = gate_limit;
   p.tokens = tokens;
   p.n_out = n_out;
   p.ld_out = ld_out;

@@ -3,7 +3,7 @@
 //
 //   scores  s = softmax(z) over all experts, z the router's logits in 32-bit
 //   choice  the `top` largest scores of a token (ties: the smaller index)
-//   weights the chosen scores over their sum (+ 1e-20)
+//   weights the chosen scores over their sum (+ 1e-20), or (renorm 0) the chosen scores as they are
 //   out[t]  = sum over the chosen of weight * expert's result  (+ sigmoid(g_t) * shared expert's result)
 //
 // The grouped matrix products between these kernels read rows through `row_src` and pick a tile's matrix
@@ -22,7 +22,7 @@ constexpr int kWarps = kThreads / 32;
 __global__ void __launch_bounds__(kThreads) moe_route_kernel(int* __restrict__ chosen, float* __restrict__ weight,
                                                              float* __restrict__ shared_gate,
                                                              const float* __restrict__ logits, int ld, int tokens,
-                                                             int E, int top, int gate_col) {
+                                                             int E, int top, int gate_col, int renorm) {
   extern __shared__ float scores[];      // [kWarps][E]
   pdl_trigger();
   pdl_wait();
@@ -64,8 +64,10 @@ __global__ void __launch_bounds__(kThreads) moe_route_kernel(int* __restrict__ c
     __syncwarp();
   }
   __syncwarp();
-  const float inv = 1.f / (total + 1e-20f);
-  for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] *= inv;
+  if (renorm) {
+    const float inv = 1.f / (total + 1e-20f);
+    for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] *= inv;
+  }
   if (lane == 0 && shared_gate != nullptr) shared_gate[t] = gate_col >= 0 ? 1.f / (1.f + expf(-z[gate_col])) : 1.f;
 }
 
@@ -155,11 +157,11 @@ __global__ void __launch_bounds__(kThreads) moe_combine_kernel(float* __restrict
 }  // namespace
 
 LAB_EXPORT int lab_moe_route(int* chosen, float* weight, float* shared_gate, const float* logits, int ld, int tokens,
-                             int E, int top, int gate_col, cudaStream_t stream) {
+                             int E, int top, int gate_col, int renorm, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || (size_t)kWarps * E * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
   lab_launch(moe_route_kernel, dim3((tokens + kWarps - 1) / kWarps), dim3(kThreads), sizeof(float) * kWarps * E, stream,
-             chosen, weight, shared_gate, logits, ld, tokens, E, top, gate_col);
+             chosen, weight, shared_gate, logits, ld, tokens, E, top, gate_col, renorm);
   LAB_LAUNCH_CHECK();
 }
 

@@ -188,14 +188,14 @@ __global__ void __launch_bounds__(1024) stream_add_norm_kernel(
 }
 
 // ---- embedding + learned position ---------------------------------------------------------
-// out[t] = table[id_t] + positions[p_t] as a 32-bit row.
+// out[t] = table[id_t] * scale + positions[p_t] as a 32-bit row.
 template <typename T>
 __global__ void __launch_bounds__(kThreads) embed_position_kernel(float* __restrict__ out,
                                                                   const T* __restrict__ table,
                                                                   const T* __restrict__ pos_table,
                                                                   const int* __restrict__ ids,
                                                                   const int* __restrict__ positions, int hidden,
-                                                                  int vocab, int max_positions) {
+                                                                  int vocab, int max_positions, float scale) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -203,14 +203,14 @@ __global__ void __launch_bounds__(kThreads) embed_position_kernel(float* __restr
   id = min(max(id, 0), vocab - 1);
   const T* row = table + (size_t)id * hidden;
   if (pos_table == nullptr) {      // no learned positions: the table's row as a 32-bit row
-    for (int i = threadIdx.x; i < hidden; i += kThreads) out[(size_t)t * hidden + i] = to_f32(row[i]);
+    for (int i = threadIdx.x; i < hidden; i += kThreads) out[(size_t)t * hidden + i] = to_f32(row[i]) * scale;
     return;
   }
   if (p >= max_positions && threadIdx.x == 0) lab_set_error(LAB_ERR_ROW_RANGE);
   p = min(max(p, 0), max_positions - 1);
   const T* prow = pos_table + (size_t)p * hidden;
   for (int i = threadIdx.x; i < hidden; i += kThreads)
-    out[(size_t)t * hidden + i] = to_f32(row[i]) + to_f32(prow[i]);
+    out[(size_t)t * hidden + i] = to_f32(row[i]) * scale + to_f32(prow[i]);
 }
 
 // ---- x += norm(product): the sum that closes a sublayer whose *output* is normed ----------------
@@ -374,16 +374,16 @@ LAB_EXPORT int lab_stream_add_norm(float* out_a, void* out_b, float* x, const fl
 }
 
 LAB_EXPORT int lab_embed_position(float* out, const void* table, const void* pos_table, const int* ids,
-                                  const int* positions, int tokens, int hidden, int vocab, int max_positions, int dtype,
-                                  cudaStream_t stream) {
+                                  const int* positions, int tokens, int hidden, int vocab, int max_positions, float scale,
+                                  int dtype, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (dtype == LAB_F32)
     lab_launch(embed_position_kernel<float>, dim3(tokens), dim3(kThreads), 0, stream, out,
-               (const float*)table, (const float*)pos_table, ids, positions, hidden, vocab, max_positions);
+               (const float*)table, (const float*)pos_table, ids, positions, hidden, vocab, max_positions, scale);
   else
     lab_launch(embed_position_kernel<__nv_bfloat16>, dim3(tokens), dim3(kThreads), 0, stream, out,
                (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, ids, positions, hidden, vocab,
-               max_positions);
+               max_positions, scale);
   LAB_LAUNCH_CHECK();
 }
 

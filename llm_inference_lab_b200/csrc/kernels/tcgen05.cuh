@@ -193,6 +193,16 @@ __host__ __device__ constexpr uint32_t umma_instr_desc(int m, int n, bool b_n_ma
 // fewer roundings only come closer to the exact value); exp and the division use the hardware
 // approximations (relative error about 2^-21, far below bfloat16's 2^-9).
 __device__ __forceinline__ float silu_gate(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+// The same with the capped form of the gate (`gate_pair` in common.cuh): a positive limit caps g from above and
+// u on both sides, the sigmoid reads 1.702 g and u enters as u + 1; limit 0 is silu(g) * u.
+__device__ __forceinline__ float silu_gate(float g, float u, float limit) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return __fdividef(g, 1.f + __expf(-1.702f * g)) * (u + 1.f);
+  }
+  return silu_gate(g, u);
+}
 
 // ---- host: tensor maps -----------------------------------------------------------------------
 typedef CUresult (*LabEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

@@ -266,9 +266,11 @@ def rope_kv_write_table(qkv, table, rotary_dim, slots, cache_k, cache_v, n_q, n_
 
 
 def gemm_plain(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gated: bool = False,
-               out_f32: bool = False, out: torch.Tensor | None = None, gelu: bool = False) -> torch.Tensor:
-    """out = x @ w.T (+ bias) on the ordinary arithmetic units; `gated`: silu(x@wg.T) * (x@wu.T), w = [wg; wu];
-    `gelu`: the tanh form of GELU after the bias, before the rounding."""
+               out_f32: bool = False, out: torch.Tensor | None = None, gelu: bool = False,
+               gate_limit: float = 0.0) -> torch.Tensor:
+    """out = x @ w.T (+ bias) on the ordinary arithmetic units; `gated`: silu(x@wg.T) * (x@wu.T), w = [wg; wu]
+    (`gate_limit` > 0: the capped form, see `linear_gated`); `gelu`: the tanh form of GELU after the bias, before
+    the rounding."""
     assert not (gated and gelu)
     _on_gpu(x, w, bias, out)
     M, K = x.shape
@@ -281,7 +283,7 @@ def gemm_plain(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = Non
     assert out.dtype == odt and out.stride(1) == 1 and out.shape == (M, N)
     _check(lib("gemm_plain").lab_gemm_plain(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), M, N, K, x.stride(0),
                                             out.stride(0), (1 + int(gelu)) if gelu else int(gated), dtype_code(x.dtype), int(out_f32),
-                                            _stream()),
+                                            ctypes.c_float(gate_limit), _stream()),
            "gemm_plain")
     return out
 
@@ -312,11 +314,16 @@ def linear_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.T
 def attention_plain(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tensor, row_req: torch.Tensor,
                     row_pos: torch.Tensor, block_table: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
                     window: int, scale: float, out: torch.Tensor | None = None, keep_first: int = 0,
-                    sink_one: bool = False) -> torch.Tensor:
+                    sink_one: bool = False, sink: torch.Tensor | None = None,
+                    dist_bias: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of every row over its request's pages; q may be a column slice of the fused projection.
     `keep_first`: with a window, the first that many positions stay visible; `sink_one`: one more in the
-    softmax's denominator."""
-    _on_gpu(q, cache_k, cache_v, row_req, row_pos, block_table)
+    softmax's denominator; `sink` [n_q] 32-bit: exp(sink[h]) more instead; `dist_bias` [n_q, L] 32-bit: added to
+    the scaled score by distance query - key, distances from L - 1 on sharing the last entry."""
+    _on_gpu(q, cache_k, cache_v, row_req, row_pos, block_table, sink, dist_bias)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() >= n_q and sink.is_contiguous())
+    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.dim() == 2 and
+                                 dist_bias.shape[0] == n_q and dist_bias.is_contiguous())
     tokens = q.shape[0]
     if out is None:
         out = torch.empty((tokens, n_q * head_dim), dtype=q.dtype, device=q.device)
@@ -326,7 +333,8 @@ def attention_plain(q: torch.Tensor, cache_k: torch.Tensor, cache_v: torch.Tenso
     _check(lib("attention_plain").lab_attention_plain(
         _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_k), _ptr(cache_v), _ptr(row_req), _ptr(row_pos),
         _ptr(block_table), block_table.shape[1], tokens, n_q, n_kv, head_dim, page_size, num_pages, window,
-        ctypes.c_float(scale), int(keep_first), int(bool(sink_one)), dtype_code(q.dtype), _stream()), "attention_plain")
+        ctypes.c_float(scale), int(keep_first), int(bool(sink_one) or sink is not None), _ptr(sink), _ptr(dist_bias),
+        dist_bias.shape[1] if dist_bias is not None else 0, dtype_code(q.dtype), _stream()), "attention_plain")
     return out
 
 
@@ -406,7 +414,7 @@ def force_plain(flag: bool) -> bool:
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gated: bool = False,
             out_f32: bool = False, swap: bool | None = None, bn: int | None = None, splits: int = 1,
-            out: torch.Tensor | None = None, gelu: bool = False) -> torch.Tensor:
+            out: torch.Tensor | None = None, gelu: bool = False, gate_limit: float = 0.0) -> torch.Tensor:
     """out = x @ w.T (+ bias) on the tcgen05 tensor cores (bfloat16 in, 32-bit accumulate); `gelu`: the
     tanh form of GELU after the bias, before the rounding (not with `gated` or `splits`).
 
@@ -449,13 +457,14 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, 
     if gelu and (gated or splits > 1):
         raise KernelError("gemm_tc: GELU goes with the plain, unsplit product")
     _check(lib("gemm_tc").lab_gemm_tc(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), T, n_out, K, x.stride(0), ld_out,
-                                      (1 + int(gelu)) if gelu else int(gated), int(f32), int(swap), bn, splits, _stream()), "gemm_tc")
+                                      (1 + int(gelu)) if gelu else int(gated), int(f32), int(swap), bn, splits,
+                                      ctypes.c_float(gate_limit), _stream()), "gemm_tc")
     return out
 
 
 def gemm_tc2(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, gated: bool = False,
              out_f32: bool = False, splits: int = 1, out: torch.Tensor | None = None, bn: int = 0,
-             gelu: bool = False) -> torch.Tensor:
+             gelu: bool = False, gate_limit: float = 0.0) -> torch.Tensor:
     """out = x @ w.T (+ bias) on pairs of SMs (tcgen05.mma.cta_group::2): tiles of 256 tokens by 256
     accumulator columns, each CTA of a pair loading half of the weight tile.  For steps with many
     tokens; `splits` > 1 returns 32-bit partial products [splits, tokens, out].  `bn`: accumulator
@@ -485,7 +494,8 @@ def gemm_tc2(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
     if gelu and (gated or splits > 1):
         raise KernelError("gemm_tc2: GELU goes with the plain, unsplit product")
     _check(lib("gemm_tc2").lab_gemm_tc2(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), T, n_out, K, x.stride(0), ld_out,
-                                        (1 + int(gelu)) if gelu else int(gated), int(f32), splits, bn, _stream()), "gemm_tc2")
+                                        (1 + int(gelu)) if gelu else int(gated), int(f32), splits, bn,
+                                        ctypes.c_float(gate_limit), _stream()), "gemm_tc2")
     return out
 
 
@@ -648,17 +658,18 @@ def linear(x, w, bias=None, out_f32=False, allow_partial=False, out=None, act=No
     return gemm_tc(x, w, bias, out_f32=out_f32, out=out, gelu=gelu)
 
 
-def linear_gated(x, w_gate_up):
-    """silu(x @ wg.T) * (x @ wu.T) with w_gate_up = [wg; wu]."""
+def linear_gated(x, w_gate_up, limit: float = 0.0):
+    """silu(g) * u with g = x @ wg.T, u = x @ wu.T and w_gate_up = [wg; wu].  `limit` > 0: the capped form,
+    g' = min(g, limit), u' = clamp(u, -limit, limit), g' * sigmoid(1.702 g') * (u' + 1)."""
     if x.dtype == torch.float32 or _force_plain or not _tc_operands(x, w_gate_up):
-        return gemm_plain(x, w_gate_up, None, gated=True)
+        return gemm_plain(x, w_gate_up, None, gated=True, gate_limit=limit)
     # Pairs of SMs (256 tokens x 128 features per tile, gate rows in one CTA and up rows in the other)
     # once their tiles fill most of the 74 pairs: measured 6 to 12 % faster from there on at the 0.5B,
     # 1.5B and 7B layer sizes (2,048 tokens: 31.7 against 33.7, 76 against 85, 349 against 385 us).
     T, inter = x.shape[0], w_gate_up.shape[0] // 2
     if -(-T // 256) * (-(-inter // 128)) >= 64:
-        return gemm_tc2(x, w_gate_up, None, gated=True)
-    return gemm_tc(x, w_gate_up, None, gated=True)
+        return gemm_tc2(x, w_gate_up, None, gated=True, gate_limit=limit)
+    return gemm_tc(x, w_gate_up, None, gated=True, gate_limit=limit)
 
 
 # Which kernel serves requests that bring several tokens: "auto" (tcgen05 for heads of 64 and of 128
@@ -766,25 +777,30 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
 
 
 def attention(q, cache_k, cache_v, ctx, group, n_q, n_kv, head_dim, window, scale, chunk=0, keep_first=0,
-              sink_one=False):
+              sink_one=False, sink=None, dist_bias=None):
     """Causal attention of every row over its request's cached keys: all of them, the last `window`, or
     (with `chunk`) those of the row's own chunk of `chunk` positions, chunks counted from position 0.  The
     kernels take the mask as one number: a window as it is, a chunk as its negative.  `keep_first`: beside a
     window, the first that many positions of the sequence stay visible; `sink_one`: the softmax's denominator
-    holds one more (a key with score 0 and no value)."""
+    holds one more (a key with score 0 and no value); `sink` [n_q] 32-bit: it holds exp(sink[h]) more instead (a
+    learned score of that key, unscaled); `dist_bias` [n_q, L] 32-bit: a number per head and distance query - key
+    added to the scaled score, distances from L - 1 on sharing the last entry."""
+    if sink is not None:
+        sink_one = False
     if chunk:
         if window:
             raise KernelError("attention takes a window or a chunk, not both")
         window = -int(chunk)
     if keep_first and window <= 0:
         keep_first = 0          # kept first positions only matter beside a window
-    if q.dtype == torch.bfloat16 and not _force_plain and attention_tc_supported(head_dim):
+    if q.dtype == torch.bfloat16 and not _force_plain and attention_tc_supported(head_dim) and dist_bias is None:
         # the denominator's extra one is a sink of 0 for every head
         return attention_tc(q, cache_k, cache_v, ctx.q_start, ctx.kv_len, ctx.pos0, group.block_table,
                             ctx.n_requests, ctx.q_lens, ctx.max_kv_len, n_q, n_kv, head_dim, window, scale,
-                            keep_first=keep_first, sink=_zero_sinks(q.device, n_q) if sink_one else None)
+                            keep_first=keep_first,
+                            sink=sink if sink is not None else (_zero_sinks(q.device, n_q) if sink_one else None))
     return attention_plain(q, cache_k, cache_v, ctx.row_req, ctx.row_pos, group.block_table, n_q, n_kv, head_dim,
-                           window, scale, keep_first=keep_first, sink_one=sink_one)
+                           window, scale, keep_first=keep_first, sink_one=sink_one, sink=sink, dist_bias=dist_bias)
 
 
 _zero_sink_cache: dict = {}
@@ -1122,8 +1138,8 @@ def latent_attention_plain_form(q: torch.Tensor, cache: torch.Tensor, w_up: torc
 # A 32-bit stream with learned positions and normed sublayer outputs (csrc/kernels/stream32.cu).
 # ----------------------------------------------------------------------------------------
 def embed_position(ids: torch.Tensor, positions: torch.Tensor | None, table: torch.Tensor,
-                   pos_table: torch.Tensor | None) -> torch.Tensor:
-    """32-bit rows table[id] + pos_table[position]; without a position table, table[id] alone."""
+                   pos_table: torch.Tensor | None, scale: float = 1.0) -> torch.Tensor:
+    """32-bit rows table[id] * scale + pos_table[position]; without a position table, table[id] * scale alone."""
     _on_gpu(ids, positions, table, pos_table)
     tokens, (vocab, hidden) = ids.numel(), table.shape
     assert ids.dtype == torch.int32 and table.is_contiguous()
@@ -1134,7 +1150,7 @@ def embed_position(ids: torch.Tensor, positions: torch.Tensor | None, table: tor
     _check(lib("stream32").lab_embed_position(_ptr(out), _ptr(table), _ptr(pos_table), _ptr(ids),
                                               _ptr(positions if pos_table is not None else None), tokens, hidden,
                                               vocab, pos_table.shape[0] if pos_table is not None else 0,
-                                              dtype_code(table.dtype), _stream()), "embed_position")
+                                              ctypes.c_float(scale), dtype_code(table.dtype), _stream()), "embed_position")
     return out
 
 
@@ -1434,10 +1450,10 @@ def selective_scan(x: torch.Tensor, dt_pre: torch.Tensor, bc: torch.Tensor, b_at
 # ----------------------------------------------------------------------------------------
 # Routed feed-forward layers (csrc/kernels/moe.cu and the grouped products).
 # ----------------------------------------------------------------------------------------
-def moe_route(logits: torch.Tensor, experts: int, top: int, gate_col: int = -1):
+def moe_route(logits: torch.Tensor, experts: int, top: int, gate_col: int = -1, renorm: bool = True):
     """From 32-bit router logits [tokens, >= experts] (column `gate_col` >= 0: the logit of a shared expert's
     gate): (chosen experts [tokens, top] int32, their weights [tokens, top], sigmoid of the gate's logit
-    [tokens] or None)."""
+    [tokens] or None).  The weights are the chosen scores over their sum, or (`renorm` False) as they are."""
     _on_gpu(logits)
     tokens = logits.shape[0]
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[1] >= experts
@@ -1445,7 +1461,7 @@ def moe_route(logits: torch.Tensor, experts: int, top: int, gate_col: int = -1):
     weight = torch.empty((tokens, top), dtype=torch.float32, device=logits.device)
     gate = torch.empty((tokens,), dtype=torch.float32, device=logits.device) if gate_col >= 0 else None
     _check(lib("moe").lab_moe_route(_ptr(chosen), _ptr(weight), _ptr(gate), _ptr(logits), logits.stride(0), tokens,
-                                    experts, top, gate_col, _stream()), "moe_route")
+                                    experts, top, gate_col, int(bool(renorm)), _stream()), "moe_route")
     return chosen, weight, gate
 
 
@@ -1527,7 +1543,7 @@ def moe_gather(x: torch.Tensor, row_src: torch.Tensor, top: int) -> torch.Tensor
 
 
 def linear_grouped_tc(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, gated: bool = False,
-                      out_f32: bool = False, bn: int | None = None) -> torch.Tensor:
+                      out_f32: bool = False, bn: int | None = None, gate_limit: float = 0.0) -> torch.Tensor:
     """Row r of the result is x[r] times the matrix w[tile_group[r // 128]] transposed, on the tcgen05 tensor cores;
     x [rows, K] bfloat16 with rows a multiple of 128, w as for `linear_grouped`.  Rows of tiles whose group is -1
     are left unwritten."""
@@ -1541,18 +1557,21 @@ def linear_grouped_tc(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor
     if bn is None:
         bn = 256 if gated else 128
     _check(lib("gemm_tc").lab_gemm_tc_grouped(_ptr(out), _ptr(x), _ptr(w), rows, N, K, x.stride(0), out.stride(0),
-                                              int(gated), int(out_f32), bn, w.shape[0], _ptr(tile_group), _stream()),
+                                              int(gated), int(out_f32), bn, w.shape[0], _ptr(tile_group),
+                                              ctypes.c_float(gate_limit), _stream()),
            "gemm_tc_grouped")
     return out
 
 
-def moe_experts_up(x: torch.Tensor, w_gate_up: torch.Tensor, lay: MoeLayout, top: int) -> torch.Tensor:
-    """silu(W_gate h) * (W_up h) of every pair's token with its expert's matrices, [rows, expert_ff] in the layout."""
+def moe_experts_up(x: torch.Tensor, w_gate_up: torch.Tensor, lay: MoeLayout, top: int, limit: float = 0.0) -> torch.Tensor:
+    """silu(W_gate h) * (W_up h) of every pair's token with its expert's matrices, [rows, expert_ff] in the layout
+    (`limit` > 0: the capped form of the gate, see `linear_gated`)."""
     if lay.tc:
-        return linear_grouped_tc(moe_gather(x, lay.row_src, top), w_gate_up, lay.tile_group, gated=True)
+        return linear_grouped_tc(moe_gather(x, lay.row_src, top), w_gate_up, lay.tile_group, gated=True, gate_limit=limit)
     if lay.few:
-        return linear_grouped_few(x, w_gate_up, lay.row_src, top, True, lay.tile_group, lay.tile, gated=True)
-    return linear_grouped(x, w_gate_up, lay.row_src, top, lay.tile_group, lay.rows, gated=True)
+        return linear_grouped_few(x, w_gate_up, lay.row_src, top, True, lay.tile_group, lay.tile, gated=True,
+                                  gate_limit=limit)
+    return linear_grouped(x, w_gate_up, lay.row_src, top, lay.tile_group, lay.rows, gated=True, gate_limit=limit)
 
 
 def moe_experts_down(act: torch.Tensor, w_down: torch.Tensor, lay: MoeLayout) -> torch.Tensor:
@@ -1565,7 +1584,8 @@ def moe_experts_down(act: torch.Tensor, w_down: torch.Tensor, lay: MoeLayout) ->
 
 
 def linear_grouped_few(x: torch.Tensor, w: torch.Tensor, row_src: torch.Tensor, row_div: int, gather: bool,
-                       tile_group: torch.Tensor, tile: int, gated: bool = False, out_f32: bool = False) -> torch.Tensor:
+                       tile_group: torch.Tensor, tile: int, gated: bool = False, out_f32: bool = False,
+                       gate_limit: float = 0.0) -> torch.Tensor:
     """`linear_grouped` for a handful of rows: only rows whose `row_src` is not -1 are formed (the others stay
     unwritten); `gather`: row r reads x[row_src[r] // row_div], else x[r]."""
     _on_gpu(x, w, row_src, tile_group)
@@ -1578,7 +1598,7 @@ def linear_grouped_few(x: torch.Tensor, w: torch.Tensor, row_src: torch.Tensor, 
     _check(lib("gemm_plain").lab_gemm_plain_grouped_few(
         _ptr(out), _ptr(x), _ptr(w), rows, N, K, x.stride(0), out.stride(0), int(gated),
         ctypes.c_longlong(w.shape[1] * K), _ptr(row_src), int(row_div), int(gather), _ptr(tile_group), int(tile),
-        dtype_code(x.dtype), int(out_f32), _stream()), "gemm_plain_grouped_few")
+        dtype_code(x.dtype), int(out_f32), ctypes.c_float(gate_limit), _stream()), "gemm_plain_grouped_few")
     return out
 
 
@@ -1588,7 +1608,8 @@ def grouped_tile_rows() -> int:
 
 
 def linear_grouped(x: torch.Tensor, w: torch.Tensor, row_src: torch.Tensor | None, row_div: int,
-                   tile_group: torch.Tensor, rows: int, gated: bool = False, out_f32: bool = False) -> torch.Tensor:
+                   tile_group: torch.Tensor, rows: int, gated: bool = False, out_f32: bool = False,
+                   gate_limit: float = 0.0) -> torch.Tensor:
     """Row r of the result is x[row_src[r] // row_div] (row_src None: x[r]) times the matrix w[tile_group[r // tile]]
     transposed; w [groups, out, in], with `gated` [groups, 2 * out, in] (gate rows, then up rows) and the result
     silu(gate) * up.  Rows of tiles whose group is -1 are left unwritten; rows whose source is -1 read zeros."""
@@ -1602,5 +1623,191 @@ def linear_grouped(x: torch.Tensor, w: torch.Tensor, row_src: torch.Tensor | Non
     _check(lib("gemm_plain").lab_gemm_plain_grouped(
         _ptr(out), _ptr(x), _ptr(w), rows, N, K, x.stride(0), out.stride(0), int(gated),
         ctypes.c_longlong(w.shape[1] * K), _ptr(row_src), int(row_div), _ptr(tile_group), dtype_code(x.dtype),
-        int(out_f32), _stream()), "gemm_plain_grouped")
+        int(out_f32), ctypes.c_float(gate_limit), _stream()), "gemm_plain_grouped")
+    return out
+
+
+def head_prep_store(proj: torch.Tensor, bias, positions: torch.Tensor, inv_freq: torch.Tensor | None, rot_dims: int, slots,
+                    cache_k, cache_v, n_q: int, n_kv: int, dim: int, vdim: int, head: int, k_at: int, v_at: int,
+                    dtype: torch.dtype, norm_eps: float = 0.0, q_norm_w=None, k_norm_w=None, q_head_scale=None,
+                    temp_coef: float = 0.0, temp_every: int = 0) -> torch.Tensor:
+    """`rope_pairs_store` with a norm per head and temperatures on q: after the rotation (`rot_dims` 0: none) every q
+    and k head is divided by its root mean square over `dim` (`norm_eps` > 0; eps inside the root) and multiplied by
+    a weight of `dim` entries shared by the heads (`q_norm_w`, `k_norm_w`; None: no weight); q is then multiplied by
+    `q_head_scale` [n_q] (32-bit; None: 1) and, with `temp_every` > 0, by 1 + temp_coef * ln(floor((pos + 1) /
+    temp_every) + 1).  Everything in 32-bit; one rounding where q, k and v leave."""
+    _on_gpu(proj, bias, positions, inv_freq, slots, cache_k, cache_v, q_norm_w, k_norm_w, q_head_scale)
+    splits = proj.shape[0] if proj.dim() == 3 else 1
+    tokens, ld = proj.shape[-2], proj.stride(-2)       # a column slice of a wider product will do
+    assert proj.dtype == torch.float32 and proj.stride(-1) == 1 and (proj.dim() == 2 or proj.is_contiguous())
+    assert rot_dims == 0 or (inv_freq.dtype == torch.float32 and inv_freq.numel() >= rot_dims // 2)
+    assert bias is None or bias.dtype == dtype
+    for w in (q_norm_w, k_norm_w):
+        assert w is None or (w.dtype == dtype and w.numel() == dim)
+    assert q_head_scale is None or (q_head_scale.dtype == torch.float32 and q_head_scale.numel() == n_q)
+    write = slots is not None
+    n_slots = page_size = 0
+    if write:
+        assert cache_k.shape == cache_v.shape and cache_k.shape[1] == n_kv and cache_k.shape[3] == head
+        assert cache_k.dtype == dtype and cache_k.is_contiguous() and cache_v.is_contiguous()
+        page_size = cache_k.shape[2]
+        n_slots = cache_k.shape[0] * page_size
+    q = torch.empty((tokens, n_q * head), dtype=dtype, device=proj.device)
+    _check(lib("rope_pairs").lab_head_prep_store(
+        _ptr(q), _ptr(cache_k if write else None), _ptr(cache_v if write else None), _ptr(proj), splits,
+        ctypes.c_longlong(tokens * ld), ld, k_at, v_at, _ptr(bias), _ptr(positions), _ptr(inv_freq), rot_dims,
+        _ptr(slots), ctypes.c_longlong(n_slots), tokens, n_q, n_kv, dim, vdim, head, max(page_size, 1),
+        ctypes.c_float(norm_eps), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(q_head_scale), ctypes.c_float(temp_coef),
+        int(temp_every), dtype_code(dtype), _stream()), "head_prep_store")
+    return q
+
+
+# ----------------------------------------------------------------------------------------
+# A residual of several streams (csrc/kernels/hyper_stream.cu).
+# ----------------------------------------------------------------------------------------
+def hyper_max_streams() -> int:
+    return int(lib("hyper_stream").lab_hyper_max_streams())
+
+
+def hyper_expand(x: torch.Tensor, streams: int) -> torch.Tensor:
+    """X [tokens, streams, hidden] with every stream a copy of the 32-bit rows x [tokens, hidden]."""
+    _on_gpu(x)
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2
+    out = torch.empty((x.shape[0], streams, x.shape[1]), dtype=torch.float32, device=x.device)
+    _check(lib("hyper_stream").lab_hyper_expand(_ptr(out), _ptr(x), x.shape[0], streams, x.shape[1], _stream()),
+           "hyper_expand")
+    return out
+
+
+def hyper_read_norm(X: torch.Tensor, c_in: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                    rows: torch.Tensor | None = None) -> torch.Tensor:
+    """u = sum_s c_in[s] X[:, s] (`c_in` None: the plain sum), then u / rms(u) * weight, rounded to the weight's
+    storage type; `weight` one number for all coordinates or one per coordinate; `rows`: only those rows."""
+    _on_gpu(X, c_in, weight, rows)
+    tokens, S, hidden = X.shape
+    assert X.dtype == torch.float32 and X.is_contiguous()
+    assert c_in is None or (c_in.dtype == torch.float32 and c_in.numel() == S)
+    assert weight.numel() in (1, hidden)
+    n_out = tokens if rows is None else rows.numel()
+    out = torch.empty((n_out, hidden), dtype=weight.dtype, device=X.device)
+    _check(lib("hyper_stream").lab_hyper_read_norm(
+        _ptr(out), _ptr(X), _ptr(c_in), _ptr(weight), int(weight.numel() == 1 and hidden != 1), _ptr(rows), n_out,
+        tokens, S, hidden, ctypes.c_float(eps), dtype_code(weight.dtype), _stream()), "hyper_read_norm")
+    return out
+
+
+def hyper_write(X: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, c_out: torch.Tensor,
+                c_in_next: torch.Tensor | None = None, weight_next: torch.Tensor | None = None, eps: float = 0.0):
+    """X[:, r] <- sum_s mix[s, r] X[:, s] + c_out[r] * y in place, all streams from the old ones; y a 32-bit result
+    [tokens, hidden] or split-K partial products [splits, tokens, hidden] summed in order.  With `c_in_next` and
+    `weight_next` it also returns the next sublayer's input, sum_r c_in_next[r] X[:, r] over its root mean square
+    times the weight, in the same pass (else None)."""
+    _on_gpu(X, y, mix, c_out, c_in_next, weight_next)
+    tokens, S, hidden = X.shape
+    assert X.dtype == torch.float32 and X.is_contiguous() and y.dtype == torch.float32 and y.is_contiguous()
+    assert y.shape[-2:] == (tokens, hidden)
+    assert mix.dtype == torch.float32 and mix.numel() == S * S and mix.is_contiguous()
+    assert c_out.dtype == torch.float32 and c_out.numel() == S
+    splits = y.shape[0] if y.dim() == 3 else 1
+    out = None
+    if weight_next is not None:
+        assert c_in_next.dtype == torch.float32 and c_in_next.numel() == S and weight_next.numel() in (1, hidden)
+        out = torch.empty((tokens, hidden), dtype=weight_next.dtype, device=X.device)
+    code = dtype_code(weight_next.dtype) if weight_next is not None else F32
+    _check(lib("hyper_stream").lab_hyper_write(
+        _ptr(X), _ptr(out), _ptr(y), splits, _ptr(mix), _ptr(c_out), _ptr(c_in_next if out is not None else None),
+        _ptr(weight_next), int(weight_next is not None and weight_next.numel() == 1 and hidden != 1), tokens, S, hidden,
+        ctypes.c_float(eps), code, _stream()), "hyper_write")
+    return out
+
+
+def normed_sum(a: torch.Tensor, wa: torch.Tensor, ca: float, b: torch.Tensor | None, wb: torch.Tensor | None, cb: float,
+               eps: float) -> torch.Tensor:
+    """ca * a / rms(a) * wa + cb * b / rms(b) * wb in 32-bit: a and b 32-bit products [tokens, hidden] or split-K
+    partial products (summed in order), each normed over the hidden size with its own weight; b may be None."""
+    _on_gpu(a, wa, b, wb)
+    tokens, hidden = a.shape[-2:]
+    assert a.dtype == torch.float32 and a.is_contiguous() and wa.numel() == hidden
+    if b is not None:
+        assert b.dtype == torch.float32 and b.is_contiguous() and b.shape[-2:] == (tokens, hidden)
+        assert wb.numel() == hidden and wb.dtype == wa.dtype
+    out = torch.empty((tokens, hidden), dtype=torch.float32, device=a.device)
+    _check(lib("hyper_stream").lab_normed_sum(
+        _ptr(out), _ptr(a), a.shape[0] if a.dim() == 3 else 1, _ptr(wa), ctypes.c_float(ca), _ptr(b),
+        (b.shape[0] if b.dim() == 3 else 1) if b is not None else 0, _ptr(wb), ctypes.c_float(cb), tokens, hidden,
+        ctypes.c_float(eps), dtype_code(wa.dtype), _stream()), "normed_sum")
+    return out
+
+
+def scale_rows(x: torch.Tensor, c: float) -> torch.Tensor:
+    """x <- x * c in place (32-bit)."""
+    _on_gpu(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(lib("hyper_stream").lab_scale_rows(_ptr(x), ctypes.c_longlong(x.numel()), ctypes.c_float(c), _stream()),
+           "scale_rows")
+    return x
+
+
+# ----------------------------------------------------------------------------------------
+# A matrix memory with exponential gates (csrc/kernels/matrix_memory.cu) around `decay_scan`.
+# ----------------------------------------------------------------------------------------
+def memory_value_width(vdim: int) -> int:
+    """Columns a head's values take in the recurrence: vdim, one column of ones for the normaliser, and zeros up
+    to a multiple of four (16-byte rows)."""
+    return (vdim + 1 + 3) // 4 * 4
+
+
+def memory_gates(proj: torch.Tensor, v_at: int, i_at: int, f_at: int, b_i: torch.Tensor, b_f: torch.Tensor, heads: int,
+                 vdim: int, cap: float):
+    """From the 32-bit input projection: gates [tokens, 2, heads] (i = cap tanh((z_i + b_i) / cap), f =
+    logsigmoid(cap tanh((z_f + b_f) / cap))) and the values [tokens, heads * memory_value_width(vdim)] with their
+    column of ones."""
+    _on_gpu(proj, b_i, b_f)
+    tokens = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and b_i.numel() == heads and b_f.numel() == heads
+    assert b_i.dtype == b_f.dtype
+    vpad = memory_value_width(vdim)
+    gates = torch.empty((tokens, 2, heads), dtype=torch.float32, device=proj.device)
+    values = torch.empty((tokens, heads * vpad), dtype=torch.float32, device=proj.device)
+    _check(lib("matrix_memory").lab_memory_gates(
+        _ptr(gates), _ptr(values), _ptr(proj), proj.stride(0), v_at, i_at, f_at, _ptr(b_i), _ptr(b_f), tokens, heads,
+        vdim, vpad, ctypes.c_float(cap), dtype_code(b_i.dtype), _stream()), "memory_gates")
+    return gates, values
+
+
+def memory_stabilize(gates: torch.Tensor, m_state: torch.Tensor, ctx, write: bool = True) -> torch.Tensor:
+    """Walks every request's rows in order: m <- max(f + m, i) from the request's slot of `m_state` [slots, heads];
+    `gates` [tokens, 2, heads] become the state's decay exp(f + m_before - m) and the key's scale exp(i - m) of each
+    row; returns m of every row [tokens, heads].  With `write` the last m goes back to the slot."""
+    _on_gpu(gates, m_state)
+    tokens, _, heads = gates.shape
+    assert gates.dtype == torch.float32 and gates.is_contiguous()
+    assert m_state.dtype == torch.float32 and m_state.is_contiguous() and m_state.shape[1:] == (heads,)
+    m = torch.empty((tokens, heads), dtype=torch.float32, device=gates.device)
+    _check(lib("matrix_memory").lab_memory_stabilize(
+        _ptr(gates), _ptr(m), _ptr(m_state), _ptr(ctx.q_start), _ptr(ctx.state_slot), ctx.n_requests, m_state.shape[0],
+        heads, int(write), _stream()), "memory_stabilize")
+    return m
+
+
+def memory_finish(o: torch.Tensor, m: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, heads: int, vdim: int,
+                  q_scale: float, floor: float, eps: float, mult: float = 1.0, out: torch.Tensor | None = None):
+    """From the recurrence's output o [tokens, heads * memory_value_width(vdim)] (S^T q and, in column vdim, n . q,
+    both for the unscaled q): y = q_scale S^T q / (max(|q_scale n . q|, exp(-m)) + floor); every head over its root
+    mean square; times `weight` [heads * vdim], times sigmoid(gate) (32-bit column slice), times `mult`; rounded
+    to the weight's storage type."""
+    _on_gpu(o, m, gate, weight, out)
+    tokens = o.shape[0]
+    vpad = memory_value_width(vdim)
+    assert o.dtype == torch.float32 and o.is_contiguous() and o.shape[1] == heads * vpad
+    assert m.dtype == torch.float32 and m.is_contiguous() and m.shape == (tokens, heads)
+    assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == (tokens, heads * vdim)
+    assert weight.numel() == heads * vdim
+    if out is None:
+        out = torch.empty((tokens, heads * vdim), dtype=weight.dtype, device=o.device)
+    assert out.dtype == weight.dtype and out.stride(1) == 1 and out.shape == (tokens, heads * vdim)
+    _check(lib("matrix_memory").lab_memory_finish(
+        _ptr(out), out.stride(0), _ptr(o), _ptr(m), _ptr(gate), gate.stride(0), _ptr(weight), tokens, heads, vdim, vpad,
+        ctypes.c_float(q_scale), ctypes.c_float(floor), ctypes.c_float(eps), ctypes.c_float(mult),
+        dtype_code(weight.dtype), _stream()), "memory_finish")
     return out

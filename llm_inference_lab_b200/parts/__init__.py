@@ -1,6 +1,6 @@
 """Parts a model is put together from.  Importing the package registers the built-in kinds."""
-from . import (attention, block, delta, embedding, latent, linear_state, mlp, moe, norm, norm_attention,  # noqa: F401
-               reentry, rope, selective_state, window_attention)                                     # (registration)
+from . import (attention, block, delta, embedding, hyper, latent, linear_state, matrix_memory, mlp, moe,  # noqa: F401
+               norm, norm_attention, reentry, rope, selective_state, window_attention)                # (registration)
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, Block, CacheView, Embedding,
                    FeedForward, GroupView, Head, Mixer, Norm, Part, PositionEncoding, StepContext, lookup,
                    register_part)

@@ -72,7 +72,7 @@ class TokenPositionEmbedding(Embedding):
 
 
 class StreamTokenEmbedding(Embedding):
-    """x[t] = table[id_t] as a 32-bit residual stream, no scaling, no positions."""
+    """x[t] = table[id_t] * `scale` (1 where none is given) as a 32-bit residual stream, no positions."""
 
     @classmethod
     def tensors(cls, spec: PartSpec):
@@ -87,14 +87,16 @@ class StreamTokenEmbedding(Embedding):
         t = weights[spec["table"]]
         self.table = (t if t.dtype == dtype else t.to(dtype)).contiguous()
         weights[spec["table"]] = self.table      # a tied head shares this storage
+        self.scale = float(spec.get("scale", 1.0))
 
     def forward(self, token_ids, positions=None):
-        return ops.embed_position(token_ids, None, self.table, None)
+        return ops.embed_position(token_ids, None, self.table, None, scale=self.scale)
 
 
 class LinearHead(Head):
     """logits = x W^T in 32-bit, no bias; W is the embedding table when tied
-    (rust/engine/src/runner/model/qwen2/engine.rs:299-303, 1312-1319)."""
+    (rust/engine/src/runner/model/qwen2/engine.rs:299-303, 1312-1319).  Options: `softcap` (cap * tanh(logits /
+    cap)) and `scale` (logits * scale), both on the 32-bit logits."""
 
     @classmethod
     def tensors(cls, spec: PartSpec):
@@ -110,14 +112,23 @@ class LinearHead(Head):
         # logits <- cap * tanh(logits / cap) where the model caps them (monotonic: the greedy pick is
         # the same, a sampled one is not, so a capped head always forms its logits)
         self.softcap = float(spec.get("softcap") or 0.0)
+        self.scale = float(spec.get("scale", 1.0))
+        if not self.scale > 0.0:
+            raise ValueError("linear_head: the logits' scale must be positive")
+
+    @classmethod
+    def libraries(cls, spec, dtype):
+        return [("hyper_stream", {})] if float(spec.get("scale", 1.0)) != 1.0 else []
 
     def forward(self, x):
         logits = ops.linear(x, self.weight, None, out_f32=True)
+        if self.scale != 1.0:
+            logits = ops.scale_rows(logits, self.scale)
         return ops.softcap(logits, self.softcap) if self.softcap else logits
 
     def pick(self, x, temperature, seeds, positions, out=None):
         # In one pass where the tensor-core product serves: the [rows, vocab] logits are never written.
-        if not self.softcap and ops.head_pick_fusable(x, self.weight):
+        if not self.softcap and self.scale == 1.0 and ops.head_pick_fusable(x, self.weight):
             return ops.head_pick(x, self.weight, temperature, seeds, positions, out=out)
         return super().pick(x, temperature, seeds, positions, out=out)
 

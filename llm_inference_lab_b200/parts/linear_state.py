@@ -141,7 +141,11 @@ class SideBySide(Mixer):
     the caller and leave the input of their output projection in a caller's buffer (`forward_inner`, `w_in`,
     `w_o`, `out_width`) share both products: one matrix of all their input rows meets h once, and their inner
     results, each times its constant, lie side by side and meet the output matrices side by side, so the
-    weighted sum is formed inside one product."""
+    weighted sum is formed inside one product.
+
+    `out_norms` (tensor names, one per mixer) with `eps`: every mixer's result is first RMS-normed over the model
+    width with a plain weight of its own, sum_i c_i * rmsnorm_i(mixer_i(h)); the mixers then share the input
+    product only, each keeps its output product, and one kernel norms and sums (one or two mixers)."""
 
     @classmethod
     def _children(cls, spec):
@@ -149,7 +153,10 @@ class SideBySide(Mixer):
 
     @classmethod
     def tensors(cls, spec: PartSpec):
-        return [t for klass, part, _ in cls._children(spec) for t in klass.tensors(part)]
+        out = [t for klass, part, _ in cls._children(spec) for t in klass.tensors(part)]
+        for name in spec.get("out_norms") or ():
+            out.append(TensorSpec(spec.prefix + name, (spec["hidden"],), init="norm"))
+        return out
 
     @classmethod
     def cache_need(cls, spec: PartSpec):
@@ -157,7 +164,8 @@ class SideBySide(Mixer):
 
     @classmethod
     def libraries(cls, spec, dtype):
-        return [job for klass, part, _ in cls._children(spec) for job in klass.libraries(part, dtype)] + [("stream32", {})]
+        return ([job for klass, part, _ in cls._children(spec) for job in klass.libraries(part, dtype)]
+                + [("hyper_stream" if spec.get("out_norms") else "stream32", {})])
 
     def __init__(self, spec, weights, dtype, device):
         super().__init__(spec, weights, dtype, device)
@@ -166,13 +174,40 @@ class SideBySide(Mixer):
             raise ValueError("side_by_side: at least one mixer")
         self.decode_graph_safe = all(getattr(m, "decode_graph_safe", False) for m, _ in self.mixers)
         self.shared = all(hasattr(m, "forward_inner") for m, _ in self.mixers)
-        if self.shared:
+        self.out_norms = None
+        if spec.get("out_norms"):
+            names = tuple(spec["out_norms"])
+            if len(names) != len(self.mixers) or not 1 <= len(names) <= 2:
+                raise ValueError("side_by_side: out_norms names one weight per mixer, for one or two mixers")
+            self.out_norms = [self._weight(weights, n).contiguous() for n in names]
+            self.eps = float(spec["eps"])
+            if self.shared:
+                self.w_in = torch.cat([m.w_in for m, _ in self.mixers], dim=0).contiguous()
+                self.in_widths = [m.w_in.shape[0] for m, _ in self.mixers]
+        elif self.shared:
             self.w_in = torch.cat([m.w_in for m, _ in self.mixers], dim=0).contiguous()
             self.in_widths = [m.w_in.shape[0] for m, _ in self.mixers]
             self.w_o = torch.cat([m.w_o for m, _ in self.mixers], dim=1).contiguous()
             self.widths = [m.out_width for m, _ in self.mixers]
 
+    def _forward_normed(self, x, ctx: StepContext, cache: CacheView):
+        results = []
+        if self.shared:
+            proj = ops.linear(x, self.w_in, None, out_f32=True)
+            at = 0
+            for i, (mixer, _) in enumerate(self.mixers):
+                inner = mixer.forward_inner(x, ctx, cache.part(i), proj=proj[:, at: at + self.in_widths[i]])
+                results.append(ops.linear(inner, mixer.w_o, None, out_f32=True, allow_partial=True))
+                at += self.in_widths[i]
+        else:
+            results = [mixer.forward(x, ctx, cache.part(i)) for i, (mixer, _) in enumerate(self.mixers)]
+        second = len(results) > 1
+        return ops.normed_sum(results[0], self.out_norms[0], self.mixers[0][1], results[1] if second else None,
+                              self.out_norms[1] if second else None, self.mixers[1][1] if second else 0.0, self.eps)
+
     def forward(self, x, ctx: StepContext, cache: CacheView):
+        if self.out_norms is not None:
+            return self._forward_normed(x, ctx, cache)
         if self.shared:
             proj = ops.linear(x, self.w_in, None, out_f32=True)
             inner = torch.empty((x.shape[0], sum(self.widths)), dtype=self.dtype, device=x.device)

@@ -13,7 +13,10 @@ class RoutedExperts(FeedForward):
     which every token uses `top`: router logits z = W_router h in 32-bit, scores softmax(z) over all experts,
     the `top` largest chosen (ties: the smaller index), weighted by their scores over the sum of the chosen
     scores (+ 1e-20).  `shared_ff` > 0: one more expert of that many rows runs for every token and is added,
-    with `shared_gate` multiplied by sigmoid(W_sg h), one number per token.
+    with `shared_gate` multiplied by sigmoid(W_sg h), one number per token.  `renorm` False: the weights are the
+    chosen scores as they are.  `limit` > 0 (and `shared_limit` for the shared expert): the experts are of the
+    capped form W_down (g' * sigmoid(1.702 g') * (u' + 1)) with g' = min(W_gate h, limit) and u' = clamp(W_up h,
+    -limit, limit).
 
     The router's matrix and the gate's row are one product; one kernel picks, one lays the (token, expert)
     pairs out in rows grouped by expert, two grouped products run the experts, and one kernel forms the weighted
@@ -56,6 +59,8 @@ class RoutedExperts(FeedForward):
         w = lambda name: self._weight(weights, name)  # noqa: E731
         self.shared_ff = int(spec.get("shared_ff") or 0)
         self.gated_share = bool(self.shared_ff and spec.get("shared_gate"))
+        self.renorm = bool(spec.get("renorm", True))
+        self.limit, self.shared_limit = float(spec.get("limit") or 0.0), float(spec.get("shared_limit") or 0.0)
         rows = [w(n["router"])] + ([w(n["shared_gate"]).reshape(1, -1)] if self.gated_share else [])
         self.w_router = torch.cat(rows, dim=0).contiguous()
         names = [n["expert"].format(e) for e in range(self.experts)]
@@ -69,13 +74,14 @@ class RoutedExperts(FeedForward):
     def forward(self, x, ctx):
         E, top = self.experts, self.top
         logits = ops.linear(x, self.w_router, None, out_f32=True)
-        chosen, weight, gate = ops.moe_route(logits, E, top, gate_col=E if self.gated_share else -1)
+        chosen, weight, gate = ops.moe_route(logits, E, top, gate_col=E if self.gated_share else -1, renorm=self.renorm)
         lay = ops.moe_layout(chosen, E, x.dtype, x.shape[1], self.ff)
-        act = ops.moe_experts_up(x, self.w_gate_up, lay, top)
+        act = ops.moe_experts_up(x, self.w_gate_up, lay, top, limit=self.limit)
         y = ops.moe_experts_down(act, self.w_down, lay)
         shared = None
         if self.shared_ff:
-            shared = ops.linear(ops.linear_gated(x, self.w_shared_gate_up), self.w_shared_down, None, out_f32=True)
+            shared = ops.linear(ops.linear_gated(x, self.w_shared_gate_up, limit=self.shared_limit), self.w_shared_down,
+                                None, out_f32=True)
         return ops.moe_combine(y, lay.pos_of, weight, shared, gate)
 
 

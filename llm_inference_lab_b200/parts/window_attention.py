@@ -1,6 +1,9 @@
 """Grouped-query attention with rotary positions on neighbouring pairs, a window that keeps the first tokens,
-and a softmax with one more in its denominator."""
+a softmax with one more (or a learned term) in its denominator, and, as options, a norm per head on q and k,
+temperatures on q, and a learned bias by distance."""
 from __future__ import annotations
+
+import math
 
 import numpy as np
 import torch
@@ -8,6 +11,26 @@ import torch
 from ..kernels import ops
 from .base import CacheView, Mixer, StepContext, register_part
 from .spec import PagedKV, PartSpec, TensorSpec
+
+
+def distance_bucket(n: int, rows: int, far: float) -> int:
+    """The row of a distance table of `rows` rows that serves the distance n >= 0."""
+    half = rows // 2
+    if n < half or half == 0:
+        return min(n, rows - 1)
+    return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+
+
+def distance_table(rel: torch.Tensor, rows: int, far: float) -> torch.Tensor:
+    """The learned table `rel` [rows, heads] laid out by distance for the attention kernels: [heads, L] 32-bit,
+    entry n the bias of distance n; L ends where every later distance reads the last row, so the kernels clamp."""
+    if rel.shape[0] != rows or rows < 1 or not far > max(rows // 2, 1):
+        raise ValueError("pair_rope_attention: dist_bias is (rows of the table, a distance beyond rows // 2)")
+    last = 0
+    while distance_bucket(last, rows, far) < rows - 1 and last < (1 << 20):
+        last += 1
+    index = torch.tensor([distance_bucket(n, rows, far) for n in range(last + 1)], dtype=torch.long, device=rel.device)
+    return rel.to(torch.float32)[index].t().contiguous()
 
 
 class PairRopeAttention(Mixer):
@@ -21,8 +44,24 @@ class PairRopeAttention(Mixer):
     keep their true positions.  `sink_one`: the softmax's denominator holds one more, exp(0), a key without
     a value.  W_o closes.
 
-    One product forms q, k (and v) in 32-bit; one kernel adds the biases, rotates, rounds q and writes k and v
-    to their page slots.  Heads are cached `ops.padded_head(dim, vdim)` wide with zeros beyond their own size."""
+    Further options, each off unless named:
+    `rot_scaling`: every rotation frequency is divided by this factor (positions stretched linearly).
+    `head_norm` "unit": after the rotation every q and k head is divided by its root mean square over `dim`
+    (`eps` inside the root); "weight": and multiplied by a weight of `dim` entries shared by all heads (tensors
+    `q.norm`, `k.norm`).
+    `head_temp`: the score of query head h is multiplied by a learned number (tensor `temp` [heads]).
+    `q_temp` (coef, every): q at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).
+    `sink_learned`: the softmax's denominator holds exp(sink_h), a learned number per head (tensor `sink`): a key
+    without a value whose score is not scaled and gets no bias.
+    `dist_bias` (rows, far): a learned number per head is added to the scaled score by the distance n = i - j: tensor
+    `rel` [rows, heads] (rows -1: as many as the checkpoint stores), row n for n < rows // 2, else min(rows - 1, rows // 2 + floor(ln(n / (rows // 2)) /
+    ln(far / (rows // 2)) * (rows - rows // 2))): later rows share distances on a logarithmic scale that reaches
+    the last row at `far`.
+
+    One product forms q, k (and v) in 32-bit; one kernel adds the biases, rotates, norms, applies the
+    temperatures, rounds q and writes k and v to their page slots.  Heads are cached `ops.padded_head(dim, vdim)`
+    wide with zeros beyond their own size.  `forward_inner` leaves the heads' outputs for a caller that owns the
+    output projection (mixers side by side)."""
     decode_graph_safe = True
 
     @classmethod
@@ -36,6 +75,14 @@ class PairRopeAttention(Mixer):
                     TensorSpec(p + "o.b", (h,), init="bias")]
             if not spec.get("values_from_keys"):
                 out.append(TensorSpec(p + "v.b", (G * V,), init="bias"))
+        if spec.get("head_norm") == "weight":
+            out += [TensorSpec(p + "q.norm", (D,), init="norm"), TensorSpec(p + "k.norm", (D,), init="norm")]
+        if spec.get("head_temp"):
+            out.append(TensorSpec(p + "temp", (H,), init="norm"))
+        if spec.get("sink_learned"):
+            out.append(TensorSpec(p + "sink", (H,), init="bias"))
+        if spec.get("dist_bias"):
+            out.append(TensorSpec(p + "rel", (int(spec["dist_bias"][0]), H), init="bias"))
         return out
 
     @classmethod
@@ -74,12 +121,34 @@ class PairRopeAttention(Mixer):
         if self.rot_dims % 2 or not 0 <= self.rot_dims <= self.dim:
             raise ValueError("pair_rope_attention: rot_dims must be even and at most dim")
         i = np.arange(self.rot_dims // 2, dtype=np.float64)
-        inv = np.power(float(spec["rot_base"]), -2.0 * i / max(self.rot_dims, 1)).astype(np.float32)
+        inv = np.power(float(spec.get("rot_base") or 1.0), -2.0 * i / max(self.rot_dims, 1))
+        inv = (inv / float(spec.get("rot_scaling") or 1.0)).astype(np.float32)
         self.inv_freq = torch.from_numpy(inv).to(device)
+        # the options that take the kernel with a norm per head and temperatures
+        self.head_norm = spec.get("head_norm")
+        if self.head_norm not in (None, "unit", "weight"):
+            raise ValueError(f"pair_rope_attention: head_norm {self.head_norm!r} is not one of 'unit', 'weight'")
+        self.eps = float(spec.get("eps") or 0.0)
+        if self.head_norm and not self.eps > 0.0:
+            raise ValueError("pair_rope_attention: a norm per head needs eps")
+        f32 = lambda n: weights[spec.prefix + n].to(device=device, dtype=torch.float32).contiguous()  # noqa: E731
+        self.head_temp = f32("temp") if spec.get("head_temp") else None
+        self.q_temp = tuple(spec["q_temp"]) if spec.get("q_temp") else None
+        if self.q_temp is not None and (len(self.q_temp) != 2 or int(self.q_temp[1]) < 1):
+            raise ValueError("pair_rope_attention: q_temp is (coef, every) with every >= 1")
+        self.sink = f32("sink") if spec.get("sink_learned") else None
+        self.dist_bias = None
+        if spec.get("dist_bias"):
+            rows, far = int(spec["dist_bias"][0]), float(spec["dist_bias"][1])
+            rel = f32("rel")
+            self.dist_bias = distance_table(rel, rows if rows > 0 else rel.shape[0], far)     # -1: as many as stored
+        self.prep = bool(self.head_norm or self.head_temp is not None or self.q_temp is not None)
         w = lambda n: self._weight(weights, n)  # noqa: E731
         names = ("q", "k") if self.from_keys else ("q", "k", "v")
         self.w_in = torch.cat([w(n) for n in names], dim=0).contiguous()
         self.bias_in = torch.cat([w(n + ".b") for n in names], dim=0).contiguous() if spec.get("bias") else None
+        self.norm_q = w("q.norm") if self.head_norm == "weight" else None
+        self.norm_k = w("k.norm") if self.head_norm == "weight" else None
         self.k_at = self.n_q * self.dim
         self.v_at = self.k_at if self.from_keys else self.k_at + self.n_kv * self.dim
         # the heads' outputs come `head` wide: zero columns of W_o meet the padding
@@ -87,16 +156,36 @@ class PairRopeAttention(Mixer):
         w_o[:, :, : self.vdim] = w("o").view(-1, self.n_q, self.vdim)
         self.w_o = w_o.view(-1, self.n_q * self.head).contiguous()
         self.bias_o = w("o.b") if spec.get("bias") else None
+        self.out_width = self.n_q * self.head
+
+    def forward_inner(self, x: torch.Tensor, ctx: StepContext, cache: CacheView, out=None, mult: float = 1.0, proj=None):
+        """The heads' outputs side by side [tokens, heads * padded head] in the storage type: what `w_o` reads.
+        `proj`: the 32-bit product of x with `w_in`, where the caller has formed it already (as columns of a wider
+        one)."""
+        if out is not None or mult != 1.0:
+            raise ValueError("pair_rope_attention: the heads' outputs leave unscaled, in a buffer of their own")
+        group = ctx.groups[cache.group]
+        if proj is None:
+            proj = ops.linear(x, self.w_in, None, out_f32=True, allow_partial=True)
+        write = cache.write
+        slots = group.row_slot if write else None
+        if self.prep:
+            coef, every = self.q_temp if self.q_temp is not None else (0.0, 0)
+            q = ops.head_prep_store(proj, self.bias_in, ctx.row_pos, self.inv_freq, self.rot_dims, slots, cache.k,
+                                    cache.v, self.n_q, self.n_kv, self.dim, self.vdim, self.head, self.k_at, self.v_at,
+                                    self.dtype, norm_eps=self.eps if self.head_norm else 0.0,
+                                    q_norm_w=self.norm_q, k_norm_w=self.norm_k, q_head_scale=self.head_temp,
+                                    temp_coef=float(coef), temp_every=int(every))
+        else:
+            q = ops.rope_pairs_store(proj, self.bias_in, ctx.row_pos, self.inv_freq, self.rot_dims, slots, cache.k,
+                                     cache.v, self.n_q, self.n_kv, self.dim, self.vdim, self.head, self.k_at, self.v_at,
+                                     self.dtype)
+        return ops.attention(q, cache.k, cache.v, ctx, group, self.n_q, self.n_kv, self.head, self.window, self.scale,
+                             keep_first=self.keep_first, sink_one=self.sink_one, sink=self.sink,
+                             dist_bias=self.dist_bias)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
-        group = ctx.groups[cache.group]
-        proj = ops.linear(x, self.w_in, None, out_f32=True, allow_partial=True)
-        write = cache.write
-        q = ops.rope_pairs_store(proj, self.bias_in, ctx.row_pos, self.inv_freq, self.rot_dims,
-                                 group.row_slot if write else None, cache.k, cache.v, self.n_q, self.n_kv, self.dim,
-                                 self.vdim, self.head, self.k_at, self.v_at, self.dtype)
-        attn = ops.attention(q, cache.k, cache.v, ctx, group, self.n_q, self.n_kv, self.head, self.window, self.scale,
-                             keep_first=self.keep_first, sink_one=self.sink_one)
+        attn = self.forward_inner(x, ctx, cache)
         if self.bias_o is not None:
             return ops.linear(attn, self.w_o, self.bias_o, out_f32=True)
         return ops.linear(attn, self.w_o, None, out_f32=True, allow_partial=True)

@@ -72,6 +72,8 @@ def _register_builtin() -> None:
     register_architecture("Ritizen", RitizenConfig, ritizen_blueprint)
     from .config.bukatar import BukatarConfig, bukatar_blueprint
     register_architecture("Bukatar", BukatarConfig, bukatar_blueprint)
+    from .config.kupedra import KupedraConfig, kupedra_blueprint
+    register_architecture("Kupedra", KupedraConfig, kupedra_blueprint)
 
 
 _register_builtin()
