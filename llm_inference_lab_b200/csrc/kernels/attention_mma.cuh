@@ -60,11 +60,15 @@ __device__ __forceinline__ long long key_offset(const int* __restrict__ bt, int 
 //   rows of this thread: lane/4 (index 0) and lane/4 + 8 (index 1); a key j is visible to row i
 //   iff j <= hi[i] and (lo[i] <= j or j < keep): `keep` first positions of the sequence stay visible
 //   before a window.  m, l, o carry the running max (log2 units), sum and accumulator.
+//   bias0 / bias1 (bias_len > 0): a table by distance for each of the thread's two rows, in natural units;
+//   entry min(hi[i] - j, bias_len - 1) is added to the scaled score (hi[i] is the row's own position).
 template <int BN>
 __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], uint32_t ks, uint32_t vs,
                                           float (&o)[DTILES][4], float (&m)[2], float (&l)[2], int key0,
                                           const int (&lo)[2], const int (&hi)[2], float scale_log2, int lane,
-                                          bool all_visible = false, int keep = 0) {
+                                          bool all_visible = false, int keep = 0,
+                                          const float* __restrict__ bias0 = nullptr,
+                                          const float* __restrict__ bias1 = nullptr, int bias_len = 0) {
   float s[BN / 8][4];
 #pragma unroll
   for (int j = 0; j < BN / 8; ++j)
@@ -92,7 +96,9 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], uint3
       const int key = key0 + j * 8 + 2 * (lane & 3) + (e & 1);
       const int r = e >> 1;
       const bool ok = all_visible || ((key >= lo[r] || key < keep) && key <= hi[r]);
-      s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
+      float sc = s[j][e] * scale_log2;
+      if (bias_len > 0) sc = fmaf((r ? bias1 : bias0)[min(max(hi[r] - key, 0), bias_len - 1)], LOG2E, sc);
+      s[j][e] = ok ? sc : -INFINITY;
       mx[r] = fmaxf(mx[r], s[j][e]);
     }
   float corr[2], base[2];

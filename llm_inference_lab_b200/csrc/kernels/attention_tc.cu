@@ -32,11 +32,13 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
     const __nv_bfloat16* __restrict__ cache_k, const __nv_bfloat16* __restrict__ cache_v,
     const int* __restrict__ q_start, const int* __restrict__ kv_len_arr, const int* __restrict__ pos0_arr,
     const int* __restrict__ block_table, int max_blocks, int n_q, int n_kv, int page_size, int num_pages, int window,
-    float scale_log2, int min_q_len, const float* __restrict__ sink, int keep) {
+    float scale_log2, int min_q_len, const float* __restrict__ sink, int keep, const float* __restrict__ dist_bias,
+    int bias_len) {
   extern __shared__ __align__(16) uint8_t smem[];
   pdl_trigger();
   pdl_wait();
   const int b = blockIdx.z, h = blockIdx.y;
+  const float* bias_h = bias_len > 0 ? dist_bias + (size_t)h * bias_len : nullptr;
   const int qs = q_start[b], ql = q_start[b + 1] - qs;
   // Later rows see more keys: their tiles are scheduled first, so that the longest CTAs do not
   // start last.
@@ -128,7 +130,8 @@ __global__ void __launch_bounds__(PF_THREADS) attention_prefill_kernel(
       const bool all_visible = first_row + 15 < ql && t * PF_BN + PF_BN - 1 <= p0 + first_row &&
                                (window == 0 || t * PF_BN >= lab_first_key(p0 + first_row + 15, window) ||
                                 t * PF_BN + PF_BN <= keep);
-      tile_step<PF_BN>(qf, kd, kd + PF_TILE_BYTES, o, m, l, t * PF_BN, lo, hi, scale_log2, lane, all_visible, keep);
+      tile_step<PF_BN>(qf, kd, kd + PF_TILE_BYTES, o, m, l, t * PF_BN, lo, hi, scale_log2, lane, all_visible, keep,
+                       bias_h, bias_h, bias_len);
     }
     __syncthreads();  // the stage is refilled by the next iteration's prefetch
   }
@@ -194,7 +197,8 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
     __nv_bfloat16* __restrict__ cache_k, __nv_bfloat16* __restrict__ cache_v,
     const int* __restrict__ q_start, const int* __restrict__ kv_len_arr, const int* __restrict__ block_table,
     int max_blocks, int n_q, int n_kv, int page_size, int num_pages, int window, float scale_log2, int splits,
-    float* __restrict__ part_acc, float* __restrict__ part_ml, int keep, const float* __restrict__ sink) {
+    float* __restrict__ part_acc, float* __restrict__ part_ml, int keep, const float* __restrict__ sink,
+    const float* __restrict__ dist_bias, int bias_len) {
   extern __shared__ __align__(16) uint8_t smem[];
   using L = DcLayout<CLUSTER>;
   pdl_trigger();
@@ -273,6 +277,15 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[t][e] = 0.f;
   const int lo[2] = {first, first}, hi[2] = {kvl - 1, kvl - 1};
+  // a bias by distance: every row of the tile is a query head with a table of its own
+  const float* bias_r[2] = {nullptr, nullptr};
+  if (bias_len > 0) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = (lane >> 2) + 8 * r;
+      bias_r[r] = dist_bias + (size_t)(head0 + (row < n_heads ? row : 0)) * bias_len;
+    }
+  }
   if (sink != nullptr && split == 0 && warp == 0) {
     // A sink: a number per query head that joins the softmax's denominator as exp(sink), unscaled, with no
     // key and no value.  It opens the state of one warp of one split (running maximum in the scores' log2
@@ -300,7 +313,8 @@ __global__ void __launch_bounds__(DC_THREADS) attention_decode_kernel(
     const int key0 = key_of(t);
     // every key of an inner tile is visible to the one query row: no mask to evaluate
     tile_step<DC_BN>(qf, kd, kd + DC_TILE_BYTES, o, m, l, key0, lo, hi, scale_log2, lane,
-                     (key0 >= first || key0 + DC_BN <= keep) && key0 + DC_BN <= kvl, keep);
+                     (key0 >= first || key0 + DC_BN <= keep) && key0 + DC_BN <= kvl, keep, bias_r[0], bias_r[1],
+                     bias_len);
     __syncwarp();
     stage = (stage + 1) % L::STAGES;
   }
@@ -448,7 +462,8 @@ LAB_EXPORT int lab_attention_prefill(void* out, int out_stride, const void* q, i
                                      const void* cache_v, const int* q_start, const int* kv_len, const int* pos0,
                                      const int* block_table, int max_blocks, int requests, int max_q_len, int n_q,
                                      int n_kv, int page_size, int num_pages, int window, float scale, int min_q_len,
-                                     const float* sink, int keep_first, cudaStream_t stream) {
+                                     const float* sink, int keep_first, const float* dist_bias, int bias_len,
+                                     cudaStream_t stream) {
   if (requests <= 0 || max_q_len <= 0) return 0;
   if (n_q % n_kv || q_stride % 8 || (((uintptr_t)q) & 15)) return (int)cudaErrorInvalidValue;
   static bool configured = false;
@@ -462,15 +477,17 @@ LAB_EXPORT int lab_attention_prefill(void* out, int out_stride, const void* q, i
                          (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
                          (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v, q_start, kv_len, pos0,
                          block_table, max_blocks, n_q, n_kv, page_size, num_pages, window, scale * LOG2E, min_q_len,
-                         sink, window > 0 && keep_first > 0 ? keep_first : 0);
+                         sink, window > 0 && keep_first > 0 ? keep_first : 0, dist_bias, dist_bias != nullptr ? bias_len : 0);
 }
 
 static int decode_launch(void* out, int out_stride, const void* q, int q_stride, const void* cache_k,
                          const void* cache_v, const int* q_start, const int* kv_len, const int* block_table,
                          int max_blocks, int requests, int n_q, int n_kv, int page_size, int num_pages, int window,
                          float scale, int splits, float* scratch, bool may_cluster, cudaStream_t stream,
-                         int keep_first = 0, const float* sink = nullptr) {
+                         int keep_first = 0, const float* sink = nullptr, const float* dist_bias = nullptr,
+                         int bias_len = 0) {
   if (requests <= 0) return 0;
+  if (dist_bias == nullptr) bias_len = 0;
   const int keep = window > 0 && keep_first > 0 ? keep_first : 0;
   const bool cluster = may_cluster && splits >= 2 && splits <= DC_MAX_CLUSTER;
   if (n_kv <= 0 || n_q % n_kv || splits < 1 || (splits > 1 && !cluster && scratch == nullptr)) return (int)cudaErrorInvalidValue;
@@ -507,7 +524,8 @@ static int decode_launch(void* out, int out_stride, const void* q, int q_stride,
     return (int)cudaLaunchKernelEx(&cfg, attention_decode_kernel<true>, (__nv_bfloat16*)out, out_stride,
                                    (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)cache_k, (__nv_bfloat16*)cache_v,
                                    q_start, kv_len, block_table, max_blocks, n_q, n_kv, page_size, num_pages, window,
-                                   scale * LOG2E, splits, (float*)nullptr, (float*)nullptr, keep, sink);
+                                   scale * LOG2E, splits, (float*)nullptr, (float*)nullptr, keep, sink, dist_bias,
+                                   bias_len);
   }
   float* part_acc = scratch;
   float* part_ml = scratch ? scratch + (size_t)requests * n_q * splits * D : nullptr;
@@ -515,7 +533,7 @@ static int decode_launch(void* out, int out_stride, const void* q, int q_stride,
                              (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
                              (__nv_bfloat16*)cache_k, (__nv_bfloat16*)cache_v, q_start, kv_len, block_table,
                              max_blocks, n_q, n_kv, page_size, num_pages, window, scale * LOG2E, splits, part_acc,
-                             part_ml, keep, sink);
+                             part_ml, keep, sink, dist_bias, bias_len);
   if (e != cudaSuccess) return (int)e;
   if (splits > 1)
     e = lab_launch(attention_merge_kernel, dim3(requests, n_q), dim3(D), 0, stream, (__nv_bfloat16*)out, out_stride,
@@ -527,15 +545,18 @@ static int decode_launch(void* out, int out_stride, const void* q, int q_stride,
 // shared memory (worth it while all CTAs of the launch are resident at once); else the merge kernel
 // does it, from scratch: lab_attention_decode_scratch_floats(...) floats (may be null when unused).
 // keep_first: beside a window, the first that many positions stay visible; sink: null or a number per
-// query head that joins the softmax's denominator as exp(sink).
+// query head that joins the softmax's denominator as exp(sink); dist_bias: null or [n_q, bias_len] floats, a
+// number per head and distance query - key added to the scaled score (distances from bias_len - 1 on share the
+// last entry).
 LAB_EXPORT int lab_attention_decode(void* out, int out_stride, const void* q, int q_stride, const void* cache_k,
                                     const void* cache_v, const int* q_start, const int* kv_len,
                                     const int* block_table, int max_blocks, int requests, int n_q, int n_kv,
                                     int page_size, int num_pages, int window, float scale, int splits, float* scratch,
-                                    int cluster_merge, int keep_first, const float* sink, cudaStream_t stream) {
+                                    int cluster_merge, int keep_first, const float* sink, const float* dist_bias,
+                                    int bias_len, cudaStream_t stream) {
   return decode_launch(out, out_stride, q, q_stride, cache_k, cache_v, q_start, kv_len, block_table, max_blocks,
                        requests, n_q, n_kv, page_size, num_pages, window, scale, splits, scratch, cluster_merge != 0,
-                       stream, keep_first, sink);
+                       stream, keep_first, sink, dist_bias, bias_len);
 }
 
 // ----------------------------------------------------------------------------------------

@@ -15,7 +15,7 @@
 //   memory_stabilize  per request and head, over the step's rows in order: m, the decay a_t and the key scale
 //                     s_t of every row; m of the request's last row goes back to its state slot
 //   memory_finish     per row: o_t with q's scale, each head over its root mean square, the weight, the sigmoid
-//                     gate, rounded to T for the output projection
+//                     gate, rounded to T for the output projection; zeros for rows of padding (state slot -1)
 //
 // All of it is 32-bit; T says how the weights are stored and how the last result is rounded.
 #include "common.cuh"
@@ -111,13 +111,18 @@ __global__ void __launch_bounds__(kThreads) memory_finish_kernel(T* __restrict__
                                                                  const float* __restrict__ gate, int ld_g,
                                                                  const T* __restrict__ w, int tokens, int H, int V,
                                                                  int vpad, float q_scale, float floor_, float eps,
-                                                                 float mult) {
+                                                                 float mult, const int* __restrict__ row_req,
+                                                                 const int* __restrict__ state_slot) {
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long pair = (long long)blockIdx.x * (kThreads / 32) + warp;
   if (pair >= (long long)tokens * H) return;
   const int t = (int)(pair / H), h = (int)(pair - (long long)t * H);
+  if (state_slot[row_req[t]] == -1) {      // a row of padding: the recurrence left nothing for it
+    for (int e = lane; e < V; e += 32) out[(size_t)t * ld_out + h * V + e] = from_f32<T>(0.f);
+    return;
+  }
   const float* oh = o + ((size_t)t * H + h) * vpad;
   const float nq = oh[V] * q_scale;
   const float den = fmaxf(fabsf(nq), expf(-m[(size_t)t * H + h])) + floor_;
@@ -166,15 +171,15 @@ LAB_EXPORT int lab_memory_stabilize(float* gates, float* m_out, float* m_state, 
 
 LAB_EXPORT int lab_memory_finish(void* out, int ld_out, const float* o, const float* m, const float* gate, int ld_g,
                                  const void* w, int tokens, int H, int V, int vpad, float q_scale, float floor_, float eps,
-                                 float mult, int dtype, cudaStream_t stream) {
+                                 float mult, const int* row_req, const int* state_slot, int dtype, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const long long pairs = (long long)tokens * H;
   const int blocks = (int)((pairs + kThreads / 32 - 1) / (kThreads / 32));
   if (dtype == LAB_F32)
     lab_launch(memory_finish_kernel<float>, dim3(blocks), dim3(kThreads), 0, stream, (float*)out, ld_out, o, m, gate, ld_g,
-               (const float*)w, tokens, H, V, vpad, q_scale, floor_, eps, mult);
+               (const float*)w, tokens, H, V, vpad, q_scale, floor_, eps, mult, row_req, state_slot);
   else
     lab_launch(memory_finish_kernel<__nv_bfloat16>, dim3(blocks), dim3(kThreads), 0, stream, (__nv_bfloat16*)out, ld_out,
-               o, m, gate, ld_g, (const __nv_bfloat16*)w, tokens, H, V, vpad, q_scale, floor_, eps, mult);
+               o, m, gate, ld_g, (const __nv_bfloat16*)w, tokens, H, V, vpad, q_scale, floor_, eps, mult, row_req, state_slot);
   LAB_LAUNCH_CHECK();
 }

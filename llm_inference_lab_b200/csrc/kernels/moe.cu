@@ -43,23 +43,27 @@ __global__ void __launch_bounds__(kThreads) moe_route_kernel(int* __restrict__ c
   sum = warp_sum(sum);
   __syncwarp();
   float total = 0.f;
+  // A score that is no number (a row of padding may hold anything) counts as -1, below every real score and
+  // above the mark of a taken expert (-3), so that every choice names an expert that exists.
   for (int k = 0; k < top; ++k) {
-    float best = -1.f;
+    float best = -2.f;
     int at = E;
-    for (int e = lane; e < E; e += 32)
-      if (s[e] > best) { best = s[e]; at = e; }       // ascending e: the first of equals stays
+    for (int e = lane; e < E; e += 32) {
+      const float v = s[e] >= 0.f || s[e] == -3.f ? s[e] : -1.f;
+      if (v > best) { best = v; at = e; }       // ascending e: the first of equals stays
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ob = __shfl_xor_sync(0xffffffffu, best, o);
       const int oa = __shfl_xor_sync(0xffffffffu, at, o);
       if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
     }
-    const float score = best / sum;
+    const float score = best >= 0.f ? best / sum : 0.f;
     total += score;
     if (lane == 0) {
-      chosen[(size_t)t * top + k] = at;
+      chosen[(size_t)t * top + k] = min(at, E - 1);
       weight[(size_t)t * top + k] = score;
-      s[at] = -2.f;      // taken
+      if (at < E) s[at] = -3.f;      // taken
     }
     __syncwarp();
   }

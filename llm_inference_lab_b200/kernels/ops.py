@@ -720,12 +720,18 @@ def decode_splits(n_decode: int, n_kv: int, group: int, max_kv_len: int, keys_pe
 
 
 def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requests, q_lens, max_kv_len,
-                 n_q, n_kv, head_dim, window, scale, out=None, splits=None, scratch=None, keep_first=0, sink=None):
+                 n_q, n_kv, head_dim, window, scale, out=None, splits=None, scratch=None, keep_first=0, sink=None,
+                 dist_bias=None):
     """Tensor-core attention: the prefill kernel serves requests with several new tokens,
     the split-KV decode kernel those with one.  A negative `window` means chunks of that many positions.
     `keep_first`: beside a window, the first that many positions stay visible.  `sink`: 32-bit numbers, one per
-    query head, that join the softmax's denominator as exp(sink) (a key with that unscaled score and no value)."""
-    _on_gpu(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, sink)
+    query head, that join the softmax's denominator as exp(sink) (a key with that unscaled score and no value).
+    `dist_bias` [n_q, L] 32-bit: a number per head and distance query - key added to the scaled score, distances
+    from L - 1 on sharing the last entry (served by the `mma.sync` kernels)."""
+    _on_gpu(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, sink, dist_bias)
+    assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.dim() == 2 and
+                                 dist_bias.shape[0] == n_q and dist_bias.is_contiguous())
+    bias_len = dist_bias.shape[1] if dist_bias is not None else 0
     assert sink is None or (sink.dtype == torch.float32 and sink.numel() >= n_q and sink.is_contiguous())
     keep_first = int(keep_first) if window > 0 else 0
     if q.dtype != torch.bfloat16 or not attention_tc_supported(head_dim):
@@ -741,7 +747,7 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
     n_decode = sum(1 for n in q_lens if n == 1)
     use_tc05 = PREFILL_KERNEL == "tc05" or (PREFILL_KERNEL == "auto" and max_q > 64)
     if max_q > 1 and use_tc05 and head_dim in (64, 128) and page_size >= 8 and page_size <= 128 and \
-            page_size & (page_size - 1) == 0:
+            page_size & (page_size - 1) == 0 and dist_bias is None:
         # tcgen05 kernel: tiles of 128 query rows, scores and P V on the 5th-generation tensor cores
         L5 = lib("attention_tc05", {"LAB_HEAD_DIM": head_dim})
         _check(L5.lab_attention_prefill_tc05(
@@ -753,7 +759,8 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
         _check(L.lab_attention_prefill(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_k), _ptr(cache_v),
                                        _ptr(q_start), _ptr(kv_len), _ptr(pos0), _ptr(block_table),
                                        block_table.shape[1], n_requests, max_q, n_q, n_kv, page_size, num_pages,
-                                       window, ctypes.c_float(scale), 2, _ptr(sink), keep_first, _stream()),
+                                       window, ctypes.c_float(scale), 2, _ptr(sink), keep_first, _ptr(dist_bias),
+                                       bias_len, _stream()),
                "attention_prefill")
     if n_decode:
         if splits is None:
@@ -770,7 +777,8 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
         _check(L.lab_attention_decode(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_k), _ptr(cache_v),
                                       _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.shape[1],
                                       n_requests, n_q, n_kv, page_size, num_pages, window, ctypes.c_float(scale),
-                                      splits, _ptr(scratch), 1 if in_cluster else 0, keep_first, _ptr(sink), _stream()),
+                                      splits, _ptr(scratch), 1 if in_cluster else 0, keep_first, _ptr(sink),
+                                      _ptr(dist_bias), bias_len, _stream()),
                "attention_decode",
                2 if splits > 1 and not in_cluster else 1)
     return out
@@ -793,11 +801,11 @@ def attention(q, cache_k, cache_v, ctx, group, n_q, n_kv, head_dim, window, scal
         window = -int(chunk)
     if keep_first and window <= 0:
         keep_first = 0          # kept first positions only matter beside a window
-    if q.dtype == torch.bfloat16 and not _force_plain and attention_tc_supported(head_dim) and dist_bias is None:
+    if q.dtype == torch.bfloat16 and not _force_plain and attention_tc_supported(head_dim):
         # the denominator's extra one is a sink of 0 for every head
         return attention_tc(q, cache_k, cache_v, ctx.q_start, ctx.kv_len, ctx.pos0, group.block_table,
                             ctx.n_requests, ctx.q_lens, ctx.max_kv_len, n_q, n_kv, head_dim, window, scale,
-                            keep_first=keep_first,
+                            keep_first=keep_first, dist_bias=dist_bias,
                             sink=sink if sink is not None else (_zero_sinks(q.device, n_q) if sink_one else None))
     return attention_plain(q, cache_k, cache_v, ctx.row_req, ctx.row_pos, group.block_table, n_q, n_kv, head_dim,
                            window, scale, keep_first=keep_first, sink_one=sink_one, sink=sink, dist_bias=dist_bias)
@@ -1790,12 +1798,12 @@ def memory_stabilize(gates: torch.Tensor, m_state: torch.Tensor, ctx, write: boo
     return m
 
 
-def memory_finish(o: torch.Tensor, m: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, heads: int, vdim: int,
+def memory_finish(o: torch.Tensor, m: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, ctx, heads: int, vdim: int,
                   q_scale: float, floor: float, eps: float, mult: float = 1.0, out: torch.Tensor | None = None):
     """From the recurrence's output o [tokens, heads * memory_value_width(vdim)] (S^T q and, in column vdim, n . q,
     both for the unscaled q): y = q_scale S^T q / (max(|q_scale n . q|, exp(-m)) + floor); every head over its root
     mean square; times `weight` [heads * vdim], times sigmoid(gate) (32-bit column slice), times `mult`; rounded
-    to the weight's storage type."""
+    to the weight's storage type.  Rows of requests without a state slot (padding) leave as zeros."""
     _on_gpu(o, m, gate, weight, out)
     tokens = o.shape[0]
     vpad = memory_value_width(vdim)
@@ -1809,5 +1817,5 @@ def memory_finish(o: torch.Tensor, m: torch.Tensor, gate: torch.Tensor, weight: 
     _check(lib("matrix_memory").lab_memory_finish(
         _ptr(out), out.stride(0), _ptr(o), _ptr(m), _ptr(gate), gate.stride(0), _ptr(weight), tokens, heads, vdim, vpad,
         ctypes.c_float(q_scale), ctypes.c_float(floor), ctypes.c_float(eps), ctypes.c_float(mult),
-        dtype_code(weight.dtype), _stream()), "memory_finish")
+        _ptr(ctx.row_req), _ptr(ctx.state_slot), dtype_code(weight.dtype), _stream()), "memory_finish")
     return out

@@ -71,7 +71,7 @@ class MatrixMemory(Mixer):
         m = ops.memory_stabilize(gates, top.state, ctx, write=cache.write)
         o = ops.decay_scan(proj[:, :hd], proj[:, hd: 2 * hd], values, memory.state, ctx, H, H, self.dim, self.vpad,
                            a_tok=gates[:, 0, :], s_tok=gates[:, 1, :], write=cache.write)
-        return ops.memory_finish(o, m, proj[:, 2 * hd + hv: 2 * hd + 2 * hv], self.norm_weight, H, self.vdim,
+        return ops.memory_finish(o, m, proj[:, 2 * hd + hv: 2 * hd + 2 * hv], self.norm_weight, ctx, H, self.vdim,
                                  self.dim ** -0.5, self.floor, self.eps, mult=mult, out=out)
 
     def forward(self, x, ctx, cache):

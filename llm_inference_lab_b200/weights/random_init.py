@@ -38,7 +38,8 @@ def random_tensor(spec: TensorSpec, seed: int, std: float, norm_std: float, scal
     for pattern, scale in scales.items():
         if pattern in spec.name:
             values *= np.float32(scale)
-    return torch.from_numpy(np.ascontiguousarray(values, dtype=np.float32))
+    # (ascontiguousarray gives a tensor without dimensions one dimension; the shape is put back)
+    return torch.from_numpy(np.ascontiguousarray(values, dtype=np.float32)).reshape(spec.shape)
 
 
 def write_random_model(config, folder: str, seed: int = 0, dtype: torch.dtype = torch.bfloat16,

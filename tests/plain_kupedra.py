@@ -63,7 +63,7 @@ def unit_rms(x, eps):
 
 def scalar_norm(x, g, eps):
     """RMS norm whose weight is one number for all coordinates."""
-    return unit_rms(x, eps) * float(g)
+    return unit_rms(x, eps) * float(np.asarray(g).reshape(-1)[0])
 
 
 def rotate_pairs(v, positions, base, dims, factor=1.0):
@@ -98,6 +98,8 @@ def distance_bucket(n, rows, far):
     half = rows // 2
     if n < half:
         return n
+    if half == 0:            # a table of one row serves every distance
+        return 0
     return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
 
 
@@ -236,7 +238,10 @@ def run_order(cfg):
 
 def sublayer(X, w, p, q, eps, fn):
     """One sublayer on the streams X [tokens, streams, width]: read a mix of the streams, run, write back."""
-    c_in, c_out, c_mix = w[f"{p}hc{q}.in"], w[f"{p}hc{q}.out"], w[f"{p}hc{q}.mix"]
+    if f"{p}hc{q}.in" in w:
+        c_in, c_out, c_mix = w[f"{p}hc{q}.in"], w[f"{p}hc{q}.out"], w[f"{p}hc{q}.mix"]
+    else:                      # no streams configured: the plain residual x + sublayer(norm(x))
+        c_in, c_out, c_mix = np.ones(1), np.ones(1), np.ones((1, 1))
     u = np.einsum("s,tsw->tw", c_in, X)
     y = fn(scalar_norm(u, w[f"{p}norm{q}"], eps))
     return np.einsum("sr,tsw->trw", c_mix, X) + c_out[None, :, None] * y[:, None, :]
