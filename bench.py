@@ -968,6 +968,196 @@ def run_arch_bukatar(args):
     return 0
 
 
+# ----------------------------------------------------------------------------------------
+# --arch kupedra: the Kupedra design beside Bukatar and Qwen2 at equal layer sizes (random weights)
+# ----------------------------------------------------------------------------------------
+KUPEDRA_SHAPES = {
+    # width and vocabulary of the Qwen2.5 shape of the same name; attention heads as there; the matrix memory with
+    # heads x vdim = width; experts as in the Bukatar shape of the same name (a token's share has the dense
+    # feed-forward's rows); four streams
+    "0.5B": dict(heads=14, kv_heads=2, dim=64, mem_heads=14, mem_dim=64, mem_vdim=64, experts=8, top=2, expert_ff=1536,
+                 shared_ff=1792, streams=4, bias_rows=32, bias_max=1024.0),
+    "1.5B": dict(heads=12, kv_heads=2, dim=128, mem_heads=12, mem_dim=128, mem_vdim=128, experts=8, top=2, expert_ff=2816,
+                 shared_ff=3328, streams=4, bias_rows=32, bias_max=2048.0),
+}
+
+
+def kupedra_config(shape, layers):
+    """Layers alternate: the side-by-side mixer (attention with a distance table beside a matrix memory), then the
+    rotary attention; every layer with routed experts."""
+    q, m = SHAPES[shape], KUPEDRA_SHAPES[shape]
+    moe = {"kind": "moe", "router": {"experts": m["experts"], "top": m["top"]},
+           "expert": {"ff": m["expert_ff"], "limit": 7.0}, "shared": {"ff": m["shared_ff"], "limit": 7.0}}
+    D = m["dim"]
+    att = {"heads": m["heads"], "kv_heads": m["kv_heads"], "dim": D, "vdim": D}
+    kinds = [
+        lambda: {"type": "parallel", "mlp": moe,
+                 "mixer": {"left": dict(att, scale=D ** -0.5, bias_max=m["bias_max"], bias_rows=m["bias_rows"],
+                                        q_temp={"coef": 0.1, "every": 256}),
+                           "right": {"heads": m["mem_heads"], "dim": m["mem_dim"], "vdim": m["mem_vdim"], "gate_cap": 15.0}}},
+        lambda: {"type": "attention", "mlp": moe,
+                 "mixer": dict(att, scale=D ** -0.5, rot={"base": 10000.0, "dims": D // 2, "scaling": {"factor": 2.0}})},
+    ]
+    return {"architecture": "Kupedra", "vocab": q["vocab_size"], "width": q["hidden_size"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "logit_scale": 1.0, "streams": m["streams"], "max_positions": 4096,
+            "layers": [kinds[i % 2]() for i in range(layers)]}
+
+
+def kernel_points_kupedra(shape, batch, ctx_len, prefill_tokens, pk):
+    """The Kupedra design's own kernels beside the like kernels of Bukatar (the attention's store, the attention
+    itself, the sum that closes a sublayer, the experts' products), of Ritizen (the recurrence with a decay per
+    token) and of Qwen2 at the shape's sizes, each alone between CUDA events with L2 flushed: milliseconds and the
+    fraction of the roofline (measured copy bandwidth for kernels that stream, measured bf16 product rate for the
+    attention kernels and the products of a prompt)."""
+    import torch
+    from llm_inference_lab_b200.kernels import ops
+
+    dev = torch.device("cuda:0")
+    q, m, rz = SHAPES[shape], KUPEDRA_SHAPES[shape], RITIZEN_SHAPES[shape]
+    width, ff = q["hidden_size"], q["intermediate_size"]
+    flush = torch.zeros((160 << 20,), dtype=torch.int16, device=dev)
+    bw, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    rows = {}
+
+    def record(name, ms, nbytes=None, flops=None):
+        entry = {"ms": round(ms, 4)}
+        if nbytes is not None:
+            entry.update(gbs=round(nbytes / (ms / 1e3) / 1e9, 1), frac_hbm=round(nbytes / (ms / 1e3) / bw, 4))
+        if flops is not None:
+            entry.update(tflops=round(flops / (ms / 1e3) / 1e12, 2), frac_bf16=round(flops / (ms / 1e3) / tf, 4))
+        rows[name] = entry
+
+    bf = lambda *s: (0.5 * torch.randn(*s, device=dev)).to(torch.bfloat16)  # noqa: E731
+    f32 = lambda *s: 0.5 * torch.randn(*s, device=dev)  # noqa: E731
+    S = m["streams"]
+    for label, q_lens, pos0 in (("prefill", [prefill_tokens], [0]), ("decode", [1] * batch, [ctx_len] * batch)):
+        T, B = sum(q_lens), len(q_lens)
+        ctx, pages = bench_ctx(q_lens, pos0, PAGE_SIZE, dev)
+        # ---- the residual of several streams: the write of all streams with the next sublayer's read and norm
+        X, y, g1 = f32(T, S, width), f32(T, width), bf(1)
+        c_in, c_out, mix = torch.rand(S, device=dev), torch.rand(S, device=dev), torch.rand(S, S, device=dev)
+        ms = timed(lambda: ops.hyper_write(X, y, mix, c_out, c_in, g1, 1e-6), flush=flush)
+        record(f"hyper_write + next read and norm {label}", ms, nbytes=T * width * (8 * S + 4 + 2))
+        ms = timed(lambda: ops.hyper_read_norm(X, c_in, g1, 1e-6), flush=flush)
+        record(f"hyper_read_norm {label}", ms, nbytes=T * width * (4 * S + 2))
+        x, a, w1 = f32(T, width), f32(T, width), bf(width)
+        ms = timed(lambda: ops.stream_norm_add(x, a, w1, 1e-6, next_weight=w1), flush=flush)
+        record(f"bukatar stream_norm_add + next norm {label}", ms, nbytes=T * width * (4 + 4 + 4 + 2))
+        b2 = f32(T, width)
+        ms = timed(lambda: ops.normed_sum(a, w1, 0.5, b2, w1, 0.5, 1e-6), flush=flush)
+        record(f"normed_sum {label}", ms, nbytes=T * width * 12)
+        # ---- attention: rotation, norm per head, temperatures and the paged store; then the kernels with a
+        # distance table and learned sinks, beside plain causal attention with the extra one over the same pages
+        nq, nkv, D = m["heads"], m["kv_heads"], m["dim"]
+        hd = ops.padded_head(D, D)
+        ck, cv = bf(pages, nkv, PAGE_SIZE, hd), bf(pages, nkv, PAGE_SIZE, hd)
+        aproj = f32(T, (nq + 2 * nkv) * D)
+        inv, temps, wn = torch.rand(D // 4, device=dev), torch.rand(nq, device=dev), bf(D)
+        slots = ctx.groups[0].row_slot
+        ms = timed(lambda: ops.head_prep_store(aproj, None, ctx.row_pos, inv, D // 2, slots, ck, cv, nq, nkv, D, D, hd,
+                                               nq * D, (nq + nkv) * D, torch.bfloat16, norm_eps=1e-6, q_head_scale=temps),
+                   flush=flush)
+        record(f"head_prep_store rotation + unit norm + temperature {label}", ms,
+               nbytes=T * ((nq + 2 * nkv) * D * 4 + (nq + 2 * nkv) * hd * 2))
+        ms = timed(lambda: ops.head_prep_store(aproj, None, ctx.row_pos, None, 0, slots, ck, cv, nq, nkv, D, D, hd, nq * D,
+                                               (nq + nkv) * D, torch.bfloat16, norm_eps=1e-6, q_norm_w=wn, k_norm_w=wn,
+                                               temp_coef=0.1, temp_every=256), flush=flush)
+        record(f"head_prep_store weighted norm + position temperature {label}", ms,
+               nbytes=T * ((nq + 2 * nkv) * D * 4 + (nq + 2 * nkv) * hd * 2))
+        ab = bf((nq + nkv) * D)
+        ms = timed(lambda: ops.rope_pairs_store(aproj, ab, ctx.row_pos, inv, D // 2, slots, ck, cv, nq, nkv, D, D, hd,
+                                                nq * D, nq * D, torch.bfloat16), flush=flush)
+        record(f"bukatar rope_pairs_store {label}", ms, nbytes=T * ((nq + nkv) * D * 4 + (nq + 2 * nkv) * hd * 2))
+        qq = bf(T, nq * hd)
+        table, sinks = f32(nq, int(m["bias_max"]) + 1), f32(nq)
+        all_pairs = sum(sum(p + i + 1 for i in range(n)) for p, n in zip(pos0, q_lens))
+        keys = sum(p + n for p, n in zip(pos0, q_lens))
+        for name, kw in (("causal + one", dict(sink_one=True)), ("distance table + learned sink", dict(sink=sinks, dist_bias=table)),
+                         ("learned sink", dict(sink=sinks))):
+            ms = timed(lambda: ops.attention(qq, ck, cv, ctx, ctx.groups[0], nq, nkv, hd, 0, D ** -0.5, **kw), flush=flush)
+            record(f"attention {name} {label}", ms, nbytes=keys * 2 * nkv * hd * 2 + 2 * T * nq * hd * 2,
+                   flops=4.0 * all_pairs * nq * hd)
+        # ---- the matrix memory: gates, the walk of the running maximum, the recurrence, the finish; beside
+        # Ritizen's state-space walk (the same recurrence kernel with a decay per token)
+        H, N, V = m["mem_heads"], m["mem_dim"], m["mem_vdim"]
+        vpad = ops.memory_value_width(V)
+        mproj = f32(T, 2 * H * N + 2 * H * V + 2 * H)
+        b_i = bf(H)
+        S_state, m_state = torch.zeros(B, H, N, vpad, device=dev), torch.zeros(B, H, device=dev)
+
+        def memory():
+            gates, values = ops.memory_gates(mproj, 2 * H * N, 2 * H * N + 2 * H * V, 2 * H * N + 2 * H * V + H, b_i, b_i, H, V, 15.0)
+            mm = ops.memory_stabilize(gates, m_state, ctx)
+            o = ops.decay_scan(mproj[:, : H * N], mproj[:, H * N: 2 * H * N], values, S_state, ctx, H, H, N, vpad,
+                               a_tok=gates[:, 0, :], s_tok=gates[:, 1, :])
+            return ops.memory_finish(o, mm, mproj[:, 2 * H * N + H * V: 2 * H * N + 2 * H * V], bf(H * V), ctx, H, V,
+                                     N ** -0.5, 1e-6, 1e-6)
+
+        ms = timed(memory, flush=flush)
+        mem_bytes = T * (2 * H * N + 2 * H * V + 2 * H) * 4 + T * H * vpad * 8 + T * H * V * 2 + 2 * S_state.numel() * 4
+        record(f"matrix memory (gates, maximum, recurrence, finish) {label}", ms, nbytes=mem_bytes,
+               flops=None if label == "decode" else 4.0 * T * H * N * vpad)
+        gates, values = ops.memory_gates(mproj, 2 * H * N, 2 * H * N + 2 * H * V, 2 * H * N + 2 * H * V + H, b_i, b_i, H, V, 15.0)
+        ms = timed(lambda: ops.memory_stabilize(gates.clone(), m_state, ctx), flush=flush)
+        record(f"memory_stabilize (with a copy of the gates) {label}", ms)
+        ms = timed(lambda: ops.decay_scan(mproj[:, : H * N], mproj[:, H * N: 2 * H * N], values, S_state, ctx, H, H, N, vpad,
+                                          a_tok=gates[:, 0, :], s_tok=gates[:, 1, :]), flush=flush)
+        record(f"matrix memory, the recurrence alone {label}", ms,
+               nbytes=T * (2 * H * N + 2 * H * vpad + 2 * H) * 4 + 2 * S_state.numel() * 4,
+               flops=None if label == "decode" else 4.0 * T * H * N * vpad)
+        H2, N2, V2, G2 = rz["ssm_heads"], rz["ssm_state"], rz["ssm_vdim"], rz["ssm_groups"]
+        conv = f32(T, H2 * V2 + 2 * G2 * N2)
+        a_tok, s_tok = torch.rand(T, H2, device=dev), torch.rand(T, H2, device=dev)
+        state2 = torch.zeros(B, H2, N2, V2, device=dev)
+        ms = timed(lambda: ops.decay_scan(conv[:, H2 * V2 + G2 * N2:], conv[:, H2 * V2: H2 * V2 + G2 * N2], conv[:, : H2 * V2],
+                                          state2, ctx, H2, G2, N2, V2, a_tok=a_tok, s_tok=s_tok), flush=flush)
+        record(f"ritizen decay_scan decay per token {label}", ms,
+               nbytes=T * (2 * G2 * N2 + 2 * H2 * V2 + 2 * H2) * 4 + 2 * state2.numel() * 4,
+               flops=None if label == "decode" else 4.0 * T * H2 * N2 * V2)
+        # ---- the experts: the capped gate in the products' epilogues beside the SiLU gate
+        xb = bf(T, width)
+        w_gu = bf(2 * ff, width)
+        for name, limit in (("capped", 7.0), ("qwen2 SiLU", 0.0)):
+            ms = timed(lambda: ops.linear_gated(xb, w_gu, limit=limit), flush=flush)
+            record(f"gated product, {name} gate {label}", ms, nbytes=(2 * ff * width + T * (width + ff)) * 2,
+                   flops=4.0 * T * ff * width)
+        E, top, F = m["experts"], m["top"], m["expert_ff"]
+        logits = f32(T, E + 1)
+        ms = timed(lambda: ops.moe_route(logits, E, top, gate_col=E, renorm=False), flush=flush)
+        record(f"moe_route, scores as they are {label}", ms, nbytes=T * ((E + 1) * 4 + top * 8 + 4))
+        chosen, weight, gate = ops.moe_route(logits, E, top, gate_col=E, renorm=False)
+        lay = ops.moe_layout(chosen, E, torch.bfloat16, width, F)
+        w_egu = bf(E, 2 * F, width)
+        used = min(E, T * top)
+        for name, limit in (("capped", 7.0), ("bukatar SiLU", 0.0)):
+            ms = timed(lambda: ops.moe_experts_up(xb, w_egu, lay, top, limit=limit), flush=flush)
+            record(f"grouped gated product, {name} gate {label}", ms,
+                   nbytes=(used * 2 * F * width + T * width + T * top * F) * 2, flops=4.0 * T * top * F * width)
+    ops.take_device_errors()
+    return rows
+
+
+def run_arch_kupedra(args):
+    shape, layers = args.shape, args.layers or 4
+    pk, pk_src = peaks()
+    qcfg = dict(SHAPES[shape], num_hidden_layers=layers)
+    folders = {"kupedra": arch_folder(kupedra_config(shape, layers), f"kupedra_{shape}_L{layers}"),
+               "bukatar": arch_folder(bukatar_config(shape, layers), f"bukatar_{shape}_L{layers}"),
+               "qwen2": model_folder(SHAPES[shape], layers)}
+    clocks = ClockSampler()
+    with clocks:
+        models = {name: model_points(folder, args.batch, args.prompt_len, PREFILL_TOKENS, 20)
+                  for name, folder in folders.items()}
+        kernels = kernel_points_kupedra(shape, args.batch, args.prompt_len + 512, PREFILL_TOKENS, pk)
+    print(json.dumps({
+        "arch": "kupedra", "beside": ["bukatar", "qwen2"], "shape": shape, "layers": layers, "batch": args.batch,
+        "prompt_len": args.prompt_len, "prefill_tokens": PREFILL_TOKENS, "dtype": "bf16",
+        "data": "synthetic: random weights N(0, 0.02) seed 0", "kupedra_mixers": KUPEDRA_SHAPES[shape],
+        "hidden": qcfg["hidden_size"], "intermediate": qcfg["intermediate_size"], "vocab": qcfg["vocab_size"],
+        "models": models, "kernels": kernels, "peaks": dict(pk, source=pk_src), "clocks": clocks.summary()}))
+    return 0
+
+
 def kv_bytes_per_token(cfg, layers):
     d = cfg["hidden_size"] // cfg["num_attention_heads"]
     return 2 * layers * 2 * cfg["num_key_value_heads"] * d
@@ -996,12 +1186,12 @@ def main() -> int:
     ap.add_argument("--stack-stamps", action="store_true",
                     help="run a few eager decode steps with the decode stack's in-kernel clock on and print what "
                          "each kind of phase took")
-    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "sogulix", "ritizen", "bukatar"],
+    ap.add_argument("--arch", default="qwen2", choices=["qwen2", "sogulix", "ritizen", "bukatar", "kupedra"],
                     help="sogulix: instead of the headline run, prefill and decode throughput of the Sogulix design "
                          "beside Qwen2 at the layer sizes of --shape (0.5B or 1.5B; --layers, default 4), and each "
                          "of its kernels beside Qwen2's like kernel; prints its own line.  ritizen: the same for the "
                          "Ritizen design, beside Sogulix and Qwen2; bukatar: the same for the Bukatar design, beside "
-                         "Ritizen and Qwen2")
+                         "Ritizen and Qwen2; kupedra: the same for the Kupedra design, beside Bukatar and Qwen2")
     ap.add_argument("--only-prefill", type=int, default=0, metavar="TOKENS",
                     help="run only a prefill of TOKENS tokens a few times and print its time (for profiling)")
     args = ap.parse_args()
@@ -1043,6 +1233,10 @@ def main() -> int:
             ap.error("--arch bukatar knows the shapes " + ", ".join(sorted(BUKATAR_SHAPES)))
         args.layers = 0 if args.layers == cfg["num_hidden_layers"] else args.layers
         return run_arch_bukatar(args)
+    if args.arch == "kupedra":
+        if args.shape not in KUPEDRA_SHAPES:
+            ap.error("--arch kupedra knows the shapes " + ", ".join(sorted(KUPEDRA_SHAPES)))
+        return run_arch_kupedra(args)
     folder = model_folder(cfg, args.layers)
     pk, pk_src = peaks()
     if args.serve:

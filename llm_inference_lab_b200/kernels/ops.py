@@ -1138,7 +1138,7 @@ def latent_attention_plain_form(q: torch.Tensor, cache: torch.Tensor, w_up: torc
     _check(LA.lab_attention_prefill(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(pools[0]), _ptr(pools[1]),
                                     _ptr(ctx.q_start), _ptr(ctx.kv_len), _ptr(ctx.pos0), _ptr(table), table.shape[1],
                                     ctx.n_requests, ctx.max_q_len, heads, heads, page_size, num_pages, window,
-                                    ctypes.c_float(scale), int(at_least), _ptr(sink), 0, _stream()), "attention_prefill")
+                                    ctypes.c_float(scale), int(at_least), _ptr(sink), 0, None, 0, _stream()), "attention_prefill")
     return out
 
 
