@@ -1236,6 +1236,7 @@ def main() -> int:
     if args.arch == "kupedra":
         if args.shape not in KUPEDRA_SHAPES:
             ap.error("--arch kupedra knows the shapes " + ", ".join(sorted(KUPEDRA_SHAPES)))
+        args.layers = 0 if args.layers == cfg["num_hidden_layers"] else args.layers
         return run_arch_kupedra(args)
     folder = model_folder(cfg, args.layers)
     pk, pk_src = peaks()

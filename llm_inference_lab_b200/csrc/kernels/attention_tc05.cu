@@ -58,7 +58,11 @@ constexpr int OFF_Q = 0;
 constexpr int OFF_K = OFF_Q + Q_BYTES;
 constexpr int OFF_V = OFF_K + KV_STAGES * KV_TILE;
 constexpr int OFF_BAR = OFF_V + KV_STAGES * KV_TILE;
-constexpr int SMEM = OFF_BAR + 256 + 1024;
+// A bias by distance (a number per head and distance query - key, added to the scaled score) waits in shared
+// memory as one head's table, up to BIAS_MAX entries, already divided by the scale: it is added to the raw scores.
+constexpr int BIAS_MAX = 4096;
+constexpr int OFF_BIAS = OFF_BAR + 256;
+constexpr int SMEM = OFF_BIAS + BIAS_MAX * 4 + 1024;
 // tensor memory columns: two S buffers (32-bit scores), then one O of D columns.  P (bfloat16 pairs:
 // 128 keys in 64 columns) lies in the first 64 columns of the S buffer it came from.
 constexpr int TM_S = 0, TM_O = 2 * BN, TMEM_COLS = 512;
@@ -82,7 +86,8 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
     const __nv_bfloat16* __restrict__ cache_k, const __nv_bfloat16* __restrict__ cache_v,
     const int* __restrict__ q_start, const int* __restrict__ kv_len_arr, const int* __restrict__ pos0_arr,
     const int* __restrict__ block_table, int max_blocks, int n_q, int n_kv, int page_size, int num_pages, int window,
-    float scale_log2, int min_q_len, int keep, const float* __restrict__ sink) {
+    float scale_log2, int min_q_len, int keep, const float* __restrict__ sink, const float* __restrict__ dist_bias,
+    int bias_len, float bias_mult) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   Barriers* bar = reinterpret_cast<Barriers*>(smem + OFF_BAR);
@@ -291,6 +296,12 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
     const int hi = row_valid ? pos : -1;
     const int lo = lab_first_key(pos, window);
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    float* bias_s = reinterpret_cast<float*>(smem + OFF_BIAS);
+    if (bias_len > 0) {
+      // this head's table, in units of the raw scores (a weight: no kernel of the step writes it)
+      for (int i = quarter * 32 + lane; i < bias_len; i += 128) bias_s[i] = dist_bias[(size_t)h * bias_len + i] * bias_mult;
+      asm volatile("bar.sync 2, 128;" ::: "memory");      // the four softmax warps
+    }
     {
       // O accumulates in tensor memory over all tiles, relative to a reference maximum m_ref per row
       // (log2 units); l is the running sum relative to m_ref.  m_ref follows the true maximum lazily: only when a row's maximum has grown by more than RESCALE (a factor
@@ -314,6 +325,12 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_tc05_kernel(
         for (int c = 0; c < BN / 32; ++c) tmem_ld32_issue(lane_addr + TM_S + sb * BN + c * 32, sr + c * 32);
         tmem_wait();
         const int key0 = tile_of(j) * BN;
+        if (bias_len > 0) {
+          const int d0 = pos - key0;      // the distance to the tile's first key; consecutive rows read consecutive entries
+#pragma unroll
+          for (int c = 0; c < BN; ++c)
+            sr[c] = __float_as_uint(__uint_as_float(sr[c]) + bias_s[min(max(d0 - c, 0), bias_len - 1)]);
+        }
         const bool all_visible = (key0 >= lo || key0 + BN <= keep) && key0 + BN - 1 <= hi;
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
         if (all_visible) {
@@ -438,14 +455,19 @@ LAB_EXPORT int lab_attention_tc05_supports(int page_size) {
 
 // Arguments as lab_attention_prefill; total_rows is the number of rows of q (for the TMA bounds).
 // keep_first: beside a window, the first that many positions stay visible; sink: null or a number per
-// query head that joins the softmax's denominator as exp(sink).
+// query head that joins the softmax's denominator as exp(sink); dist_bias: null or [n_q, bias_len] floats
+// (bias_len up to lab_attention_tc05_bias_max()), a number per head and distance query - key added to the scaled
+// score, distances from bias_len - 1 on sharing the last entry.
+LAB_EXPORT int lab_attention_tc05_bias_max() { return BIAS_MAX; }
 LAB_EXPORT int lab_attention_prefill_tc05(void* out, int out_stride, const void* q, int q_stride, int total_rows,
                                           const void* cache_k, const void* cache_v, const int* q_start,
                                           const int* kv_len, const int* pos0, const int* block_table, int max_blocks,
                                           int requests, int max_q_len, int n_q, int n_kv, int page_size, int num_pages,
                                           int window, float scale, int min_q_len, int keep_first, const float* sink,
-                                          cudaStream_t stream) {
+                                          const float* dist_bias, int bias_len, cudaStream_t stream) {
   if (requests <= 0 || max_q_len <= 0) return 0;
+  if (dist_bias == nullptr) bias_len = 0;
+  if (bias_len < 0 || bias_len > BIAS_MAX || !(scale > 0.f)) return (int)cudaErrorInvalidValue;
   if (!lab_attention_tc05_supports(page_size) || n_q % n_kv || q_stride % 8 || (((uintptr_t)q) & 15) ||
       (((uintptr_t)cache_k) & 15) || (((uintptr_t)cache_v) & 15))
     return (int)cudaErrorInvalidValue;
@@ -466,5 +488,6 @@ LAB_EXPORT int lab_attention_prefill_tc05(void* out, int out_stride, const void*
   return (int)lab_launch(attention_prefill_tc05_kernel, grid, dim3(THREADS), (size_t)SMEM, stream, mq, mk, mv,
                          (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)cache_k, (const __nv_bfloat16*)cache_v,
                          q_start, kv_len, pos0, block_table, max_blocks, n_q, n_kv, page_size, num_pages, window,
-                         scale * LOG2E, min_q_len, window > 0 && keep_first > 0 ? keep_first : 0, sink);
+                         scale * LOG2E, min_q_len, window > 0 && keep_first > 0 ? keep_first : 0, sink, dist_bias, bias_len,
+                         1.0f / scale);
 }

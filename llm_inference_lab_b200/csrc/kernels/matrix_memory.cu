@@ -74,21 +74,24 @@ __global__ void __launch_bounds__(kThreads) memory_stabilize_kernel(float* __res
     if (lane == 0) lab_set_error(LAB_ERR_PAGE_RANGE);
     return;
   }
+  // Lanes beyond the request's rows hold (f, i) = (0, -inf), which leaves m as it is: every chunk walks all 32
+  // lanes, so the chain unrolls and its shuffles are issued ahead of it.
   float m = m_state[(size_t)slot * H + h];
-  float gi = 0.f, gf = 0.f;
+  float gi = -INFINITY, gf = 0.f;
   if (lane < n) {
     gi = gates[(size_t)(t0 + lane) * 2 * H + h];
     gf = gates[(size_t)(t0 + lane) * 2 * H + H + h];
   }
   for (int c = 0; c < n; c += 32) {
-    float gi_next = 0.f, gf_next = 0.f;
+    float gi_next = -INFINITY, gf_next = 0.f;
     if (c + 32 + lane < n) {
       gi_next = gates[(size_t)(t0 + c + 32 + lane) * 2 * H + h];
       gf_next = gates[(size_t)(t0 + c + 32 + lane) * 2 * H + H + h];
     }
     const int cnt = min(32, n - c);
     float carried_mine = 0.f, m_mine = 0.f;
-    for (int j = 0; j < cnt; ++j) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
       const float carried = __shfl_sync(0xffffffffu, gf, j) + m;
       m = fmaxf(carried, __shfl_sync(0xffffffffu, gi, j));
       if (j == lane) carried_mine = carried, m_mine = m;

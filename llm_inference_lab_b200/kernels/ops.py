@@ -719,6 +719,9 @@ def decode_splits(n_decode: int, n_kv: int, group: int, max_kv_len: int, keys_pe
     return int(max(1, min(room, -(-max_kv_len // (2 * keys_per_round)), 32)))
 
 
+TC05_BIAS_MAX = 4096     # entries of a distance table the tcgen05 prefill kernel holds (its BIAS_MAX)
+
+
 def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requests, q_lens, max_kv_len,
                  n_q, n_kv, head_dim, window, scale, out=None, splits=None, scratch=None, keep_first=0, sink=None,
                  dist_bias=None):
@@ -727,7 +730,8 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
     `keep_first`: beside a window, the first that many positions stay visible.  `sink`: 32-bit numbers, one per
     query head, that join the softmax's denominator as exp(sink) (a key with that unscaled score and no value).
     `dist_bias` [n_q, L] 32-bit: a number per head and distance query - key added to the scaled score, distances
-    from L - 1 on sharing the last entry (served by the `mma.sync` kernels)."""
+    from L - 1 on sharing the last entry (the tcgen05 kernel keeps a head's table in shared memory, up to
+    `TC05_BIAS_MAX` entries; longer tables run on the `mma.sync` prefill kernel)."""
     _on_gpu(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, sink, dist_bias)
     assert dist_bias is None or (dist_bias.dtype == torch.float32 and dist_bias.dim() == 2 and
                                  dist_bias.shape[0] == n_q and dist_bias.is_contiguous())
@@ -747,13 +751,14 @@ def attention_tc(q, cache_k, cache_v, q_start, kv_len, pos0, block_table, n_requ
     n_decode = sum(1 for n in q_lens if n == 1)
     use_tc05 = PREFILL_KERNEL == "tc05" or (PREFILL_KERNEL == "auto" and max_q > 64)
     if max_q > 1 and use_tc05 and head_dim in (64, 128) and page_size >= 8 and page_size <= 128 and \
-            page_size & (page_size - 1) == 0 and dist_bias is None:
+            page_size & (page_size - 1) == 0 and bias_len <= TC05_BIAS_MAX:
         # tcgen05 kernel: tiles of 128 query rows, scores and P V on the 5th-generation tensor cores
         L5 = lib("attention_tc05", {"LAB_HEAD_DIM": head_dim})
         _check(L5.lab_attention_prefill_tc05(
             _ptr(out), out.stride(0), _ptr(q), q.stride(0), tokens, _ptr(cache_k), _ptr(cache_v), _ptr(q_start),
             _ptr(kv_len), _ptr(pos0), _ptr(block_table), block_table.shape[1], n_requests, max_q, n_q, n_kv,
-            page_size, num_pages, window, ctypes.c_float(scale), 2, keep_first, _ptr(sink), _stream()),
+            page_size, num_pages, window, ctypes.c_float(scale), 2, keep_first, _ptr(sink), _ptr(dist_bias), bias_len,
+            _stream()),
             "attention_prefill_tc05")
     elif max_q > 1:
         _check(L.lab_attention_prefill(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_k), _ptr(cache_v),
