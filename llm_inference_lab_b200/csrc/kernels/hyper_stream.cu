@@ -87,8 +87,10 @@ __global__ void __launch_bounds__(kThreads) hyper_read_norm_kernel(T* __restrict
     out[(size_t)blockIdx.x * hidden + i] = from_f32<T>(row[i] * inv * weight_at(w, w_scalar, i));
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kThreads) hyper_write_kernel(float* __restrict__ X, T* __restrict__ out,
+// SMAX bounds the streams the instance serves (2, 4 or kMaxStreams): the loops over streams unroll to it, and the
+// instances for few streams keep few registers, so that more rows are in flight on an SM.
+template <typename T, int SMAX>
+__global__ void __launch_bounds__(kThreads, SMAX <= 4 ? 5 : 3) hyper_write_kernel(float* __restrict__ X, T* __restrict__ out,
                                                                const float* __restrict__ y, int y_splits,
                                                                long long split_stride, const float* __restrict__ mix,
                                                                const float* __restrict__ c_out,
@@ -111,16 +113,16 @@ __global__ void __launch_bounds__(kThreads) hyper_write_kernel(float* __restrict
   float ss = 0.f;
   for (int i = threadIdx.x; i < hidden; i += kThreads) {
     const float yi = sum_splits(y, y_splits, split_stride, (size_t)t * hidden + i);
-    float old[kMaxStreams];
+    float old[SMAX];
 #pragma unroll
-    for (int s = 0; s < kMaxStreams; ++s) old[s] = s < S ? x[(size_t)s * hidden + i] : 0.f;
+    for (int s = 0; s < SMAX; ++s) old[s] = s < S ? x[(size_t)s * hidden + i] : 0.f;
     float u = 0.f;
 #pragma unroll
-    for (int r = 0; r < kMaxStreams; ++r) {
+    for (int r = 0; r < SMAX; ++r) {
       if (r >= S) break;
       float v = 0.f;
 #pragma unroll
-      for (int s = 0; s < kMaxStreams; ++s)
+      for (int s = 0; s < SMAX; ++s)
         if (s < S) v = fmaf(coef.mix[s * S + r], old[s], v);
       v = fmaf(coef.c_out[r], yi, v);
       x[(size_t)r * hidden + i] = v;
@@ -185,6 +187,28 @@ template <typename K>
 void allow_smem(K kernel, size_t smem) {
   if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
 }
+
+template <typename T, int SMAX>
+int launch_write(float* X, void* out, const float* y, int y_splits, const float* mix, const float* c_out,
+                 const float* c_in_next, const void* w_next, int w_scalar, int tokens, int S, int hidden, float eps,
+                 cudaStream_t stream) {
+  const size_t smem = (size_t)hidden * sizeof(float);
+  allow_smem(hyper_write_kernel<T, SMAX>, smem);
+  return (int)lab_launch(hyper_write_kernel<T, SMAX>, dim3(tokens), dim3(kThreads), smem, stream, X, (T*)out, y, y_splits,
+                         (long long)tokens * hidden, mix, c_out, c_in_next, (const T*)w_next, w_scalar, S, hidden, eps);
+}
+
+template <typename T>
+int launch_write_for(int S, float* X, void* out, const float* y, int y_splits, const float* mix, const float* c_out,
+                     const float* c_in_next, const void* w_next, int w_scalar, int tokens, int hidden, float eps,
+                     cudaStream_t stream) {
+  if (S <= 2)
+    return launch_write<T, 2>(X, out, y, y_splits, mix, c_out, c_in_next, w_next, w_scalar, tokens, S, hidden, eps, stream);
+  if (S <= 4)
+    return launch_write<T, 4>(X, out, y, y_splits, mix, c_out, c_in_next, w_next, w_scalar, tokens, S, hidden, eps, stream);
+  return launch_write<T, kMaxStreams>(X, out, y, y_splits, mix, c_out, c_in_next, w_next, w_scalar, tokens, S, hidden, eps,
+                                      stream);
+}
 }  // namespace
 
 LAB_EXPORT int lab_hyper_max_streams() { return kMaxStreams; }
@@ -221,17 +245,11 @@ LAB_EXPORT int lab_hyper_write(float* X, void* out, const float* y, int y_splits
   if (tokens <= 0) return 0;
   const size_t smem = (size_t)hidden * sizeof(float);
   if (S < 1 || S > kMaxStreams || smem > 200 * 1024 || y_splits < 1) return (int)cudaErrorInvalidValue;
-  const long long stride = (long long)tokens * hidden;
-  if (dtype == LAB_F32) {
-    allow_smem(hyper_write_kernel<float>, smem);
-    lab_launch(hyper_write_kernel<float>, dim3(tokens), dim3(kThreads), smem, stream, X, (float*)out, y, y_splits, stride,
-               mix, c_out, c_in_next, (const float*)w_next, w_scalar, S, hidden, eps);
-  } else {
-    allow_smem(hyper_write_kernel<__nv_bfloat16>, smem);
-    lab_launch(hyper_write_kernel<__nv_bfloat16>, dim3(tokens), dim3(kThreads), smem, stream, X, (__nv_bfloat16*)out, y,
-               y_splits, stride, mix, c_out, c_in_next, (const __nv_bfloat16*)w_next, w_scalar, S, hidden, eps);
-  }
-  LAB_LAUNCH_CHECK();
+  if (dtype == LAB_F32)
+    return launch_write_for<float>(S, X, out, y, y_splits, mix, c_out, c_in_next, w_next, w_scalar, tokens, hidden, eps,
+                                   stream);
+  return launch_write_for<__nv_bfloat16>(S, X, out, y, y_splits, mix, c_out, c_in_next, w_next, w_scalar, tokens, hidden,
+                                         eps, stream);
 }
 
 LAB_EXPORT int lab_normed_sum(float* out, const float* a, int a_splits, const void* wa, float ca, const float* b,

@@ -53,15 +53,16 @@ __global__ void __launch_bounds__(kThreads) memory_gates_kernel(float* __restric
 }
 
 // One warp per (request, head) walks the request's rows 32 at a time: every lane loads one row's gates, all lanes
-// follow the chain m <- max(f + m, i) through the 32 rows by shuffles (the same operations in the same order as a
-// walk row by row, so a row's m does not depend on how the sequence was cut), each lane keeps the m before and
-// after its own row and forms that row's two exponentials.  The next 32 rows' gates are loaded before the chain.
+// follow the chain m <- max(f + m, i) through the 32 rows (the same operations in the same order as a walk row
+// by row, so a row's m does not depend on how the sequence was cut), each lane keeps the m before and after its
+// own row and forms that row's two exponentials.
 // decay[t, h] and scale[t, h] leave as rows of [tokens, 2, H] (over the gates).
 __global__ void __launch_bounds__(kThreads) memory_stabilize_kernel(float* __restrict__ gates, float* __restrict__ m_out,
                                                                     float* __restrict__ m_state,
                                                                     const int* __restrict__ q_start,
                                                                     const int* __restrict__ state_slot, int requests,
                                                                     int n_slots, int H, int write) {
+  __shared__ __align__(16) float chunk_gates[kThreads / 32][64];      // per warp: 32 forget gates, then 32 input gates
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -75,34 +76,55 @@ __global__ void __launch_bounds__(kThreads) memory_stabilize_kernel(float* __res
     return;
   }
   // Lanes beyond the request's rows hold (f, i) = (0, -inf), which leaves m as it is: every chunk walks all 32
-  // lanes, so the chain unrolls and its shuffles are issued ahead of it.
+  // lanes, so the chain unrolls and its shuffles are issued ahead of it.  Rows come in groups of kAhead chunks:
+  // the next group's gates are loaded before the current group's chains, which hides the loads' latency.
+  constexpr int kAhead = 4;
+  float* mine = chunk_gates[warp];
   float m = m_state[(size_t)slot * H + h];
-  float gi = -INFINITY, gf = 0.f;
-  if (lane < n) {
-    gi = gates[(size_t)(t0 + lane) * 2 * H + h];
-    gf = gates[(size_t)(t0 + lane) * 2 * H + H + h];
-  }
-  for (int c = 0; c < n; c += 32) {
-    float gi_next = -INFINITY, gf_next = 0.f;
-    if (c + 32 + lane < n) {
-      gi_next = gates[(size_t)(t0 + c + 32 + lane) * 2 * H + h];
-      gf_next = gates[(size_t)(t0 + c + 32 + lane) * 2 * H + H + h];
-    }
-    const int cnt = min(32, n - c);
-    float carried_mine = 0.f, m_mine = 0.f;
+  float gi[kAhead], gf[kAhead], gi_next[kAhead], gf_next[kAhead];
+  auto load = [&](int first, float (&to_i)[kAhead], float (&to_f)[kAhead]) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const float carried = __shfl_sync(0xffffffffu, gf, j) + m;
-      m = fmaxf(carried, __shfl_sync(0xffffffffu, gi, j));
-      if (j == lane) carried_mine = carried, m_mine = m;
+    for (int k = 0; k < kAhead; ++k) {
+      const int row = first + k * 32 + lane;
+      const bool in = row < n;
+      to_i[k] = in ? gates[(size_t)(t0 + row) * 2 * H + h] : -INFINITY;
+      to_f[k] = in ? gates[(size_t)(t0 + row) * 2 * H + H + h] : 0.f;
     }
-    if (lane < cnt) {
-      float* g = gates + (size_t)(t0 + c + lane) * 2 * H;
-      g[h] = expf(carried_mine - m_mine);       // decay of the state
-      g[H + h] = expf(gi - m_mine);             // scale of the new key
-      m_out[(size_t)(t0 + c + lane) * H + h] = m_mine;
+  };
+  load(0, gi, gf);
+  for (int c = 0; c < n; c += kAhead * 32) {
+    load(c + kAhead * 32, gi_next, gf_next);
+#pragma unroll
+    for (int k = 0; k < kAhead; ++k) {
+      // the chunk's gates go through shared memory: every lane reads all 32 pairs, four at a time, ahead of the
+      // chain (shuffles would put their latency on it)
+      __syncwarp();
+      mine[lane] = gf[k];
+      mine[32 + lane] = gi[k];
+      __syncwarp();
+      float carried_mine = 0.f, m_mine = 0.f;
+#pragma unroll
+      for (int j4 = 0; j4 < 8; ++j4) {
+        const float4 f4 = reinterpret_cast<const float4*>(mine)[j4];
+        const float4 i4 = reinterpret_cast<const float4*>(mine + 32)[j4];
+        const float fs[4] = {f4.x, f4.y, f4.z, f4.w}, is[4] = {i4.x, i4.y, i4.z, i4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float carried = fs[e] + m;
+          m = fmaxf(carried, is[e]);
+          if (4 * j4 + e == lane) carried_mine = carried, m_mine = m;
+        }
+      }
+      const int row = c + k * 32 + lane;
+      if (row < n) {
+        float* g = gates + (size_t)(t0 + row) * 2 * H;
+        g[h] = expf(carried_mine - m_mine);       // decay of the state
+        g[H + h] = expf(gi[k] - m_mine);          // scale of the new key
+        m_out[(size_t)(t0 + row) * H + h] = m_mine;
+      }
     }
-    gi = gi_next, gf = gf_next;
+#pragma unroll
+    for (int k = 0; k < kAhead; ++k) gi[k] = gi_next[k], gf[k] = gf_next[k];
   }
   if (write && lane == 0) m_state[(size_t)slot * H + h] = m;
 }
