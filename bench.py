@@ -996,7 +996,7 @@ def kupedra_config(shape, layers):
                                         q_temp={"coef": 0.1, "every": 256}),
                            "right": {"heads": m["mem_heads"], "dim": m["mem_dim"], "vdim": m["mem_vdim"], "gate_cap": 15.0}}},
         lambda: {"type": "attention", "mlp": moe,
-                 "mixer": dict(att, scale=D ** -0.5, rot={"base": 10000.0, "dims": D // 2, "scaling": {"factor": 2.0}})},
+                 "mixer": dict(att, scale=D ** -0.5, rot={"base": 10000.0, "dims": D // 2, "scaling": {"factor": 4.0}})},
     ]
     return {"architecture": "Kupedra", "vocab": q["vocab_size"], "width": q["hidden_size"], "norm": {"eps": 1e-6},
             "embedding": {"scale": 1.0}, "logit_scale": 1.0, "streams": m["streams"], "max_positions": 4096,

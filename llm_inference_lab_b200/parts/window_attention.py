@@ -24,7 +24,7 @@ def distance_bucket(n: int, rows: int, far: float) -> int:
 def distance_table(rel: torch.Tensor, rows: int, far: float) -> torch.Tensor:
     """The learned table `rel` [rows, heads] laid out by distance for the attention kernels: [heads, L] 32-bit,
     entry n the bias of distance n; L ends where every later distance reads the last row, so the kernels clamp."""
-    if rel.shape[0] != rows or rows < 1 or not far > max(rows // 2, 1):
+    if rel.shape[0] != rows or rows < 1 or (rows // 2 >= 1 and not far > rows // 2):
         raise ValueError("pair_rope_attention: dist_bias is (rows of the table, a distance beyond rows // 2)")
     last = 0
     while distance_bucket(last, rows, far) < rows - 1 and last < (1 << 20):

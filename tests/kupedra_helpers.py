@@ -59,12 +59,12 @@ SMALL_B = config([attention(2, 2, 32, 8, 32, base=2000.0, scale=0.2, ff=moe(1, 1
 # C: a width that is no multiple of 8 (the products leave the tensor cores), no streams (the plain residual),
 # nothing rotated, one head everywhere, the loop over the last layer alone and three times, a distance table
 # that is never exhausted (far beyond the sequences)
-SMALL_C = config([attention(1, 1, 48, 20, 0, scale=0.15, ff=moe(3, 2, 10, 1.5)),
-                  parallel((1, 1, 24, 12, 0.25, (1.0, 16), 12, 5000), (1, 8, 12, 12.0), ff=moe(2, 1, 6, 3.0, (10, 3.0)))],
+SMALL_C = config([attention(1, 1, 40, 20, 0, scale=0.15, ff=moe(3, 2, 10, 1.6)),
+                  parallel((1, 1, 24, 12, 0.25, (1.0, 16), 12, 5000), (1, 8, 12, 11.0), ff=moe(2, 1, 6, 3.0, (10, 3.0)))],
                  vocab=67, width=50, eps=3e-6, streams=0, loop=(1, 2, 3))
 # D: heads of 64 entries with long portions, many experts, four streams
-SMALL_D = config([parallel((4, 2, 64, 64, 0.125, (0.3, 50), 32, 200), (2, 64, 64, 10.0), ff=moe(16, 4, 32, 1.5, (32, 2.0))),
-                  attention(4, 1, 64, 64, 32, base=250000.0, factor=4.0, scale=0.11, ff=moe(8, 2, 64, 1.0))],
+SMALL_D = config([parallel((4, 2, 64, 64, 0.125, (0.35, 50), 32, 200), (2, 64, 64, 10.0), ff=moe(16, 4, 32, 1.4, (32, 2.2))),
+                  attention(4, 1, 64, 64, 32, base=500000.0, factor=4.0, scale=0.11, ff=moe(8, 2, 64, 1.0))],
                  vocab=113, width=64, streams=4)
 SMALL = {"A": (SMALL_A, dict(seed=21, page_size=16)), "B": (SMALL_B, dict(seed=22, page_size=4)),
          "C": (SMALL_C, dict(seed=23, page_size=32)), "D": (SMALL_D, dict(seed=24, page_size=16))}
@@ -106,7 +106,7 @@ def random_config(rng):
         dim, vdim = min(size(1, 12), 160), min(size(1, 12), 160)
         if rng.random() < 0.45:
             layers.append(attention(H, G, dim, vdim, 2 * int(rng.integers(0, dim // 2 + 1)),
-                                    base=float(rng.choice([100.0, 10000.0, 250000.0])),
+                                    base=float(rng.choice([100.0, 10000.0, 500000.0])),
                                     factor=float(rng.choice([1.0, 2.0, 8.0])) if rng.random() < 0.7 else None,
                                     scale=float(rng.uniform(0.5, 2.0)) * dim ** -0.5, ff=ff()))
         else:
@@ -114,7 +114,7 @@ def random_config(rng):
             far = float(rows // 2 + int(rng.choice([1, 3, 20, 400])))
             qt = (float(rng.uniform(0.0, 1.0)), int(rng.choice([1, 4, 30, 1000]))) if rng.random() < 0.7 else None
             layers.append(parallel((H, G, dim, vdim, float(rng.uniform(0.5, 2.0)) * dim ** -0.5, qt, rows, far),
-                                   (int(rng.integers(1, 5)), size(1, 9), size(1, 9), float(rng.choice([3.0, 12.0, 30.0]))),
+                                   (int(rng.integers(1, 5)), size(1, 9), size(1, 9), float(rng.choice([3.0, 11.0, 30.0]))),
                                    ff=ff()))
     n = len(layers)
     loop = None
